@@ -1,0 +1,319 @@
+"""Benchmark of the hot path: FP8 (e4m3) paged-KV decode at the production configuration (batch 128, 64 query /
+8 kv heads, head_dim 128, page 64, contexts uniform in [1k, 32k]) plus the Gated-DeltaNet speculative step
+(batch 256, 16/32 heads, 4 draft tokens). Synthetic seeded inputs with those shapes and distributions.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl green|reference]
+
+A step is one decode call over the whole batch. ``value`` is KV bytes attended per second (algorithmic bytes
+``sum(ctx) * 2 * kv_heads * head_dim`` over the device time of the K timed steps), inputs resident in HBM;
+``e2e`` is the same quantity through the plugin call (``dispatch.with_kvcache``) with the step's inputs
+(query, page table, lengths) copied from pinned host memory and the output copied back every step; the KV
+pool is the serving cache and stays resident, as it does in the server. With N > 1 every rank owns its own
+128 requests and KV pool (requests are partitioned, no collective on the data path): weak scaling.
+
+``--impl reference`` times the reference's CPU implementation of the same path (its torch oracle,
+restated in ``oracle/attn_oracle.py``; the reference's CUDA is SM90 WGMMA and cannot be built for
+sm_100) on the host cores, each step a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from greenattention_b200 import workloads as W  # noqa: E402
+
+METRIC = "fp8_paged_decode_kv_bytes_per_s_B128"
+UNIT = "TB/s"
+WORKLOAD = "C2 production decode: B=128/GPU, QH64/KVH8, hd128, page 64, ctx~U[1k,32k], q_len 1"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001 - NVML missing: report nulls
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        med = sorted(self.samples)[len(self.samples) // 2] if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except (ValueError, IndexError):
+            return local
+    return local
+
+
+def cpu_oracle_sample(n_requests: int, seed: int, repeats: int = 1):
+    """Times the CPU oracle on a seeded sample of the decode workload; returns (TB/s, cores, description)."""
+    from oracle import attn_oracle
+
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(1024, 32769, (n_requests,), generator=g).tolist()
+    kw = W.c2_production_decode("cpu", seed=seed, lens=lens)
+    nbytes = W.attn_kv_bytes(kw)
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        attn_oracle.paged_attention(kw)
+    dt = (time.perf_counter() - t0) / repeats
+    return nbytes / dt / 1e12, cores, f"{n_requests} seeded requests ({sum(lens)} KV tokens) of the C2 workload", dt
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    times, val = [], 0.0
+    for i in range(args.warmup + args.steps):
+        val, cores, sample, dt = cpu_oracle_sample(8, seed=100 + i)
+        if i >= args.warmup:
+            times.append((val, dt))
+    value = sum(v for v, _ in times) / len(times)
+    ms = 1e3 * sum(d for _, d in times) / len(times)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 (dequantised e4m3)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "each step = CPU torch oracle over a seeded 8-request sample"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def bench_gdn(dev, steps, warmup, hbm_gbs):
+    from greenattention_b200 import gdn as gdn_mod
+    from greenattention_b200 import gdn_recurrent
+
+    gdn_mod._green_on_sm100 = lambda: True  # standalone run: no SGLang runtime context to ask
+    gdn_recurrent.ensure_ready(dev)
+    c = W.c5_gdn_spec(dev)
+    nbytes = W.gdn_bytes(c)
+    start = c["ssm_states"].clone()
+    kw = dict(q=c["q"], k=c["k"], v=c["v"], a=c["a"], b=c["b"], A_log=c["A_log"], dt_bias=c["dt_bias"],
+              ssm_states=c["ssm_states"], cache_indices=c["cache_indices"], accept_lens=c["accept_lens"])
+    out = torch.empty(c["v"].shape, dtype=torch.bfloat16, device=dev)
+    for _ in range(warmup):
+        gdn_recurrent.gdn_spec_decode(out=out, **kw)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for s, e in ev:
+        c["ssm_states"].copy_(start)
+        flush.zero_()  # 512 MB write: evicts the state from the 126 MB L2
+        s.record()
+        gdn_recurrent.gdn_spec_decode(out=out, **kw)
+        e.record()
+    torch.cuda.synchronize()
+    ms = sorted(s.elapsed_time(e) for s, e in ev)
+    med = ms[len(ms) // 2]
+    tokens = c["q"].shape[0] * c["q"].shape[1]
+    return {
+        "workload": "C5 GDN spec: B=256, H16/HV32, K=V=128, fp32 state, 4 draft tokens, accept~U{0..4}",
+        "us_per_call": med * 1e3, "verified_tok_per_s": tokens / (med * 1e-3), "algorithmic_bytes": nbytes,
+        "hbm_gbs": nbytes / (med * 1e-3) / 1e9, "hbm_frac": nbytes / (med * 1e-3) / 1e9 / hbm_gbs,
+        "l2": "flushed by a 512 MB write before each call",
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="green", choices=["green", "reference"])
+    ap.add_argument("--batch", type=int, default=128, help="requests per GPU (the named configuration uses 128)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gdn", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "green" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+
+    from greenattention_b200 import _C, attn_decode, dispatch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the green kernels have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    attn_decode.ensure_ready(dev)
+    hbm_gbs, peak_kind = peaks()
+
+    kw = W.c2_production_decode(dev, seed=2 + rank, batch=args.batch)
+    nbytes = W.attn_kv_bytes(kw)
+    run = attn_decode.select(kw)
+    if not callable(run):
+        raise SystemExit(f"decode declined: {run}")
+    out = torch.empty(kw["q"].shape, dtype=torch.bfloat16, device=dev)
+    call = dict(kw, out=out)
+    for _ in range(args.warmup):
+        run(**call)
+    torch.cuda.synchronize()
+    launches_per_step = _C.lib().ga_last_launch_count()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: K steps between two events
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            run(**call)
+        stop.record()
+        barrier()
+    ms_total = start.elapsed_time(stop)
+
+    # ---- end to end through the plugin call with host inputs
+    def stock(**_):
+        raise RuntimeError("the stock kernel must not be reached")
+
+    plugin_call = dispatch.with_kvcache(stock)
+    host = {n: kw[n].cpu().pin_memory() for n in ("q", "page_table", "cache_seqlens", "cu_seqlens_q")}
+    devbuf = {n: torch.empty_like(kw[n]) for n in host}
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = out_host.numel() * out_host.element_size()
+
+    def e2e_step():
+        for n, t in host.items():
+            devbuf[n].copy_(t, non_blocking=True)
+        res = plugin_call(**dict(kw, out=out, **devbuf))
+        out_host.copy_(res, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e_stop.record()
+    barrier()
+    e2e_ms_total = e_start.elapsed_time(e_stop)
+
+    stats = torch.tensor([ms_total, e2e_ms_total, float(nbytes)], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms_total, e2e_ms_total, total_bytes = mx[0].item(), mx[1].item(), sm[2].item()
+    else:
+        total_bytes = float(nbytes)
+    ms_step = ms_total / args.steps
+    value = total_bytes / (ms_step * 1e-3) / 1e12
+    e2e_value = total_bytes / (e2e_ms_total / args.steps * 1e-3) / 1e12
+
+    if rank == 0:
+        per_gpu_gbs = nbytes / (start.elapsed_time(stop) / args.steps * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "us_per_call": ms_step * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "requests_per_gpu": args.batch, "kv_tokens_rank0": nbytes // 2048,
+                       "partitioning": f"requests x{world}", "l2": "inputs (4.4 GB/GPU) larger than the 126 MB L2"},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms_total / args.steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": hbm_gbs, "unit": "GB/s",
+                         "frac": per_gpu_gbs / hbm_gbs, "peak_kind": f"{peak_kind} copy bandwidth",
+                         "frac_of_8TBps_nominal": per_gpu_gbs / 8000.0, "traffic": None,
+                         "kernel": "attn_rows_kernel<128,1,4,0> (+ combine, inside the same events)"},
+        }
+        if not args.no_gdn:
+            try:
+                line["gdn"] = bench_gdn(dev, max(args.steps, 10), 3, hbm_gbs)
+            except Exception as exc:  # noqa: BLE001 - the decode line must still print
+                line["gdn"] = {"error": repr(exc)}
+        if world == 1 and not args.no_cpu_baseline:
+            val, cores, sample, _ = cpu_oracle_sample(32, seed=7)
+            line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

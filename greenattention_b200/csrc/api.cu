@@ -1,0 +1,408 @@
+// C ABI of the library (declared in include/green_attention.h): argument validation, TMA descriptor
+// encoding, kernel-instance selection and launches. Replaces the reference's tvm_ffi launchers
+// (csrc/sm90/attn_decode_fp8/launcher.cu:34-214, csrc/sm90/gdn_recurrent/launcher.cu:18-177).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "../../include/green_attention.h"
+#include "attn_rows.cuh"
+#include "gdn_recurrent.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+thread_local int g_launches = 0;
+
+int fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return 1;
+}
+
+#define GA_CUDA(expr)                                                                         \
+  do {                                                                                        \
+    cudaError_t e_ = (expr);                                                                  \
+    if (e_ != cudaSuccess) return fail("%s failed: %s", #expr, cudaGetErrorString(e_));       \
+  } while (0)
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+};
+std::mutex g_mu;
+DeviceState g_dev[64];
+EncodeTiledFn g_encode = nullptr;
+
+struct MapKey {
+  const void* base;
+  long long s_page, s_tok, s_head;
+  int pages, page, kvh, hd, box_tok;
+  bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+};
+std::vector<MapEntry> g_maps;  // small most-recently-used list; guarded by g_mu
+
+// Descriptor of a paged pool [pages, page, kv_heads, head_dim] (bytes) for boxes of
+// [1 page, box_tok tokens, 1 head, 128 bytes] with the 128-byte swizzle the kernels' ldmatrix addressing expects.
+int get_map(const MapKey& key, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  for (size_t i = 0; i < g_maps.size(); ++i) {
+    if (g_maps[i].key == key) {
+      *out = g_maps[i].map;
+      return 0;
+    }
+  }
+  if (!g_encode) return fail("ga_init() has not run");
+  cuuint64_t dims[4] = {(cuuint64_t)key.hd, (cuuint64_t)key.kvh, (cuuint64_t)key.page, (cuuint64_t)key.pages};
+  cuuint64_t strides[3] = {(cuuint64_t)key.s_head, (cuuint64_t)key.s_tok, (cuuint64_t)key.s_page};
+  cuuint32_t box[4] = {128, 1, (cuuint32_t)key.box_tok, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  MapEntry e;
+  std::memset(&e, 0, sizeof(e));
+  e.key = key;
+  CUresult r = g_encode(&e.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(key.base), dims, strides, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code %d", (int)r);
+  if (g_maps.size() >= 32) g_maps.erase(g_maps.begin());
+  g_maps.push_back(e);
+  *out = e.map;
+  return 0;
+}
+
+using AttnKernel = void (*)(const ga::attn::AttnDev, const CUtensorMap, const CUtensorMap);
+
+struct AttnInstance {
+  AttnKernel fn;
+  int threads, smem, rows;
+};
+
+template <int HD, int MT, int WN, int MODE>
+AttnInstance make_instance() {
+  using C = ga::attn::Cfg<HD, MT, WN>;
+  return {ga::attn::attn_rows_kernel<HD, MT, WN, MODE>, C::THREADS, C::SMEM_BYTES, C::ROWS};
+}
+
+// Row capacity 16/32/64/128 per (request, kv head) for decode / verify; extend always uses 128 rows.
+const AttnInstance* decode_instance(int hd, int rows) {
+  static const AttnInstance t128[4] = {make_instance<128, 1, 4, 0>(), make_instance<128, 2, 2, 0>(),
+                                       make_instance<128, 4, 1, 0>(), make_instance<128, 8, 1, 0>()};
+  static const AttnInstance t256[4] = {make_instance<256, 1, 4, 0>(), make_instance<256, 2, 2, 0>(),
+                                       make_instance<256, 4, 1, 0>(), make_instance<256, 8, 1, 0>()};
+  int i = rows <= 16 ? 0 : rows <= 32 ? 1 : rows <= 64 ? 2 : 3;
+  return hd == 128 ? &t128[i] : &t256[i];
+}
+const AttnInstance* extend_instance(int hd) {
+  static const AttnInstance e128 = make_instance<128, 8, 1, 1>();
+  static const AttnInstance e256 = make_instance<256, 8, 1, 1>();
+  return hd == 128 ? &e128 : &e256;
+}
+
+int set_smem(const AttnInstance& k) {
+  GA_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(k.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               k.smem));
+  return 0;
+}
+
+constexpr size_t kWsHeader = 256;
+size_t ws_prefix_bytes(int batch) { return ((static_cast<size_t>(batch) + 1) * 4 + 255) / 256 * 256; }
+size_t ws_lse_bytes(int sm) { return static_cast<size_t>(2 * sm) * ga::attn::MAX_ROWS * 4; }
+size_t ws_o_bytes(int sm) { return static_cast<size_t>(2 * sm) * ga::attn::MAX_ROWS * 256 * 4; }
+
+int current_device(int* dev) {
+  GA_CUDA(cudaGetDevice(dev));
+  if (*dev < 0 || *dev >= 64) return fail("device index %d out of range", *dev);
+  if (!g_dev[*dev].ready) return fail("ga_init(%d) has not run", *dev);
+  return 0;
+}
+
+bool pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
+
+// Shared validation + device-struct fill for decode and extend.
+int fill_attn(const GaAttnParams* a, ga::attn::AttnDev* d, CUtensorMap* kmap, CUtensorMap* vmap) {
+  if (!a) return fail("null params");
+  if (a->head_dim != 128 && a->head_dim != 256) return fail("head_dim %d: only 128 and 256 are built", a->head_dim);
+  if (a->kv_heads <= 0 || a->q_heads <= 0 || a->q_heads % a->kv_heads) return fail("q_heads %d / kv_heads %d", a->q_heads, a->kv_heads);
+  if (!pow2(a->page_size)) return fail("page_size %d is not a power of two", a->page_size);
+  if (a->batch <= 0) return fail("batch %d", a->batch);
+  if (!a->q || !a->k_cache || !a->v_cache || !a->page_table || !a->cache_seqlens || !a->cu_seqlens_q || !a->out)
+    return fail("null tensor pointer");
+  const long long kstr[6] = {a->k_stride_page, a->k_stride_tok, a->k_stride_head,
+                             a->v_stride_page, a->v_stride_tok, a->v_stride_head};
+  for (long long s : kstr)
+    if (s % 16) return fail("k/v cache strides must be multiples of 16 bytes");
+  if ((reinterpret_cast<uintptr_t>(a->k_cache) | reinterpret_cast<uintptr_t>(a->v_cache)) & 15)
+    return fail("k/v cache base must be 16-byte aligned");
+  const int qalign = a->q_is_bf16 ? 4 : 4;  // elements: 8-byte bf16 loads, 4-byte e4m3 loads
+  if (a->q_stride_tok % qalign || a->q_stride_head % qalign ||
+      reinterpret_cast<uintptr_t>(a->q) % (a->q_is_bf16 ? 8 : 4))
+    return fail("q strides/base must allow %d-byte vector loads", a->q_is_bf16 ? 8 : 4);
+  if (a->o_stride_tok % 4 || a->o_stride_head % 4 || reinterpret_cast<uintptr_t>(a->out) % (a->out_is_f32 ? 16 : 8))
+    return fail("out strides/base must allow 4-element vector stores");
+
+  std::memset(d, 0, sizeof(*d));
+  d->q = static_cast<const uint8_t*>(a->q);
+  d->q_bf16 = a->q_is_bf16;
+  d->q_s0 = a->q_stride_tok;
+  d->q_s1 = a->q_stride_head;
+  d->k = static_cast<const uint8_t*>(a->k_cache);
+  d->v = static_cast<const uint8_t*>(a->v_cache);
+  d->k_s0 = a->k_stride_page, d->k_s1 = a->k_stride_tok, d->k_s2 = a->k_stride_head;
+  d->v_s0 = a->v_stride_page, d->v_s1 = a->v_stride_tok, d->v_s2 = a->v_stride_head;
+  d->page_shift = __builtin_ctz(a->page_size);
+  d->page_mask = a->page_size - 1;
+  d->num_pages = a->num_pages;
+  d->kvh = a->kv_heads;
+  d->gqa = a->q_heads / a->kv_heads;
+  d->pt = a->page_table;
+  d->pt_s0 = a->pt_stride_row;
+  d->pt_s1 = a->pt_stride_col;
+  d->seqlens = a->cache_seqlens;
+  d->cu = a->cu_seqlens_q;
+  d->kd = a->k_descale, d->kd_s0 = a->kd_stride_b, d->kd_s1 = a->kd_stride_h;
+  d->vd = a->v_descale, d->vd_s0 = a->vd_stride_b, d->vd_s1 = a->vd_stride_h;
+  d->out = a->out;
+  d->out_f32 = a->out_is_f32;
+  d->o_s0 = a->o_stride_tok, d->o_s1 = a->o_stride_head;
+  d->lse = a->lse;
+  d->total_q = a->total_q;
+  d->batch = a->batch;
+  d->window_left = a->window_left < 0 ? -1 : a->window_left;
+  d->scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  // TMA boxes need a swizzle-aligned (1024-byte) destination: pages of >= 8 tokens. Smaller pages are
+  // gathered row by row with 16-byte cp.async.
+  d->use_tma = a->page_size >= 8;
+  d->box_tok = a->page_size < ga::attn::TN ? a->page_size : ga::attn::TN;
+  std::memset(kmap, 0, sizeof(*kmap));
+  std::memset(vmap, 0, sizeof(*vmap));
+  if (d->use_tma) {
+    MapKey kk = {a->k_cache, a->k_stride_page, a->k_stride_tok, a->k_stride_head, a->num_pages, a->page_size,
+                 a->kv_heads, a->head_dim, d->box_tok};
+    MapKey vk = {a->v_cache, a->v_stride_page, a->v_stride_tok, a->v_stride_head, a->num_pages, a->page_size,
+                 a->kv_heads, a->head_dim, d->box_tok};
+    if (get_map(kk, kmap) || get_map(vk, vmap)) return 1;
+  }
+  return 0;
+}
+
+template <int T>
+int launch_gdn(const ga::gdn::GdnDev& d, bool bf16_state, int blocks, cudaStream_t st) {
+  if (bf16_state) ga::gdn::gdn_recurrent_kernel<T, __nv_bfloat16><<<blocks, ga::gdn::THREADS, 0, st>>>(d);
+  else ga::gdn::gdn_recurrent_kernel<T, float><<<blocks, ga::gdn::THREADS, 0, st>>>(d);
+  GA_CUDA(cudaGetLastError());
+  return 0;
+}
+
+__global__ void merge_parts_kernel(const float* o_parts, const float* lse_parts, int parts, int rows, int hd,
+                                   __nv_bfloat16* out, float* lse) {
+  const int r = blockIdx.x;
+  float mx = -INFINITY;
+  for (int s = 0; s < parts; ++s) mx = fmaxf(mx, lse_parts[s * rows + r]);
+  float den = 0.f;
+  if (mx != -INFINITY)
+    for (int s = 0; s < parts; ++s) den += expf(lse_parts[s * rows + r] - mx);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f;
+    if (mx != -INFINITY)
+      for (int s = 0; s < parts; ++s)
+        acc += expf(lse_parts[s * rows + r] - mx) * o_parts[(static_cast<long long>(s) * rows + r) * hd + d];
+    out[static_cast<long long>(r) * hd + d] = __float2bfloat16(den > 0.f ? acc / den : 0.f);
+  }
+  if (lse && threadIdx.x == 0) lse[r] = den > 0.f ? mx + logf(den) : -INFINITY;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ga_abi_version(void) { return GA_ABI_VERSION; }
+const char* ga_last_error(void) { return g_err; }
+int ga_last_launch_count(void) { return g_launches; }
+
+int ga_init(int device) {
+  if (device < 0 || device >= 64) return fail("device index %d out of range", device);
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (g_dev[device].ready) return 0;
+  }
+  int prev = 0;
+  GA_CUDA(cudaGetDevice(&prev));
+  GA_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  GA_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    cudaSetDevice(prev);
+    return fail("device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
+  }
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    GA_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || !fn) return fail("cuTensorMapEncodeTiled is not available");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  for (int hd : {128, 256}) {
+    for (int rows : {16, 32, 64, 128})
+      if (set_smem(*decode_instance(hd, rows))) return 1;
+    if (set_smem(*extend_instance(hd))) return 1;
+  }
+  GA_CUDA(cudaSetDevice(prev));
+  std::lock_guard<std::mutex> lock(g_mu);
+  g_dev[device].sm_count = prop.multiProcessorCount;
+  g_dev[device].ready = true;
+  return 0;
+}
+
+int ga_sm_count(int device) {
+  if (device < 0 || device >= 64 || !g_dev[device].ready) return -1;
+  return g_dev[device].sm_count;
+}
+
+size_t ga_attn_workspace_bytes(int device, int max_batch) {
+  int sm = (device >= 0 && device < 64 && g_dev[device].ready) ? g_dev[device].sm_count : 160;
+  return kWsHeader + ws_prefix_bytes(max_batch) + ws_lse_bytes(sm) + ws_o_bytes(sm);
+}
+
+int ga_attn_decode(const GaAttnParams* a, void* stream) {
+  int dev;
+  if (current_device(&dev)) return 1;
+  ga::attn::AttnDev d;
+  CUtensorMap kmap, vmap;
+  if (fill_attn(a, &d, &kmap, &vmap)) return 1;
+  const int rows = a->max_seqlen_q * d.gqa;
+  if (a->max_seqlen_q < 1 || rows > ga::attn::MAX_ROWS)
+    return fail("max_seqlen_q %d x GQA %d exceeds %d rows", a->max_seqlen_q, d.gqa, ga::attn::MAX_ROWS);
+  const int sm = g_dev[dev].sm_count;
+  const size_t need = kWsHeader + ws_prefix_bytes(a->batch) + ws_lse_bytes(sm) + ws_o_bytes(sm);
+  if (!a->workspace || a->workspace_bytes < need) return fail("workspace too small: %zu < %zu bytes", a->workspace_bytes, need);
+  if (reinterpret_cast<uintptr_t>(a->workspace) % 256) return fail("workspace must be 256-byte aligned");
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  d.status = reinterpret_cast<int*>(ws);
+  d.prefix = reinterpret_cast<int*>(ws + kWsHeader);
+  d.ws_lse = reinterpret_cast<float*>(ws + kWsHeader + ws_prefix_bytes(a->batch));
+  d.ws_o = reinterpret_cast<float*>(ws + kWsHeader + ws_prefix_bytes(a->batch) + ws_lse_bytes(sm));
+  d.max_q = a->max_seqlen_q;
+  d.bq = 0;
+  const AttnInstance* k = decode_instance(a->head_dim, rows);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  k->fn<<<sm, k->threads, k->smem, st>>>(d, kmap, vmap);
+  GA_CUDA(cudaGetLastError());
+  dim3 cgrid(a->batch, a->kv_heads);
+  if (a->head_dim == 128) ga::attn::attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(d, sm, k->rows);
+  else ga::attn::attn_combine_kernel<256><<<cgrid, 128, 0, st>>>(d, sm, k->rows);
+  GA_CUDA(cudaGetLastError());
+  g_launches = 2;
+  return 0;
+}
+
+int ga_attn_extend(const GaAttnParams* a, void* stream) {
+  int dev;
+  if (current_device(&dev)) return 1;
+  ga::attn::AttnDev d;
+  CUtensorMap kmap, vmap;
+  if (fill_attn(a, &d, &kmap, &vmap)) return 1;
+  if (d.gqa > ga::attn::MAX_ROWS) return fail("GQA %d exceeds %d rows", d.gqa, ga::attn::MAX_ROWS);
+  if (a->out_is_f32) return fail("extend writes bf16 only");
+  d.bq = ga::attn::MAX_ROWS / d.gqa;
+  d.max_q = 1 << 30;
+  if (!a->workspace || a->workspace_bytes < kWsHeader) return fail("workspace (status word) missing");
+  d.status = static_cast<int*>(a->workspace);
+  const long long blocks = a->total_q / d.bq + a->batch;
+  if (blocks > 0x7fffffffLL) return fail("too many query blocks");
+  if (a->total_q <= 0) {
+    g_launches = 0;
+    return 0;
+  }
+  const AttnInstance* k = extend_instance(a->head_dim);
+  dim3 grid(static_cast<unsigned>(blocks), a->kv_heads);
+  k->fn<<<grid, k->threads, k->smem, static_cast<cudaStream_t>(stream)>>>(d, kmap, vmap);
+  GA_CUDA(cudaGetLastError());
+  g_launches = 1;
+  return 0;
+}
+
+int ga_attn_merge(const GaMergeParams* m, void* stream) {
+  if (!m || !m->o_parts || !m->lse_parts || !m->out) return fail("null params");
+  if (m->parts <= 0 || m->rows <= 0 || m->head_dim <= 0) return fail("bad merge shape");
+  merge_parts_kernel<<<m->rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      m->o_parts, m->lse_parts, m->parts, m->rows, m->head_dim, static_cast<__nv_bfloat16*>(m->out), m->lse);
+  GA_CUDA(cudaGetLastError());
+  g_launches = 1;
+  return 0;
+}
+
+int ga_gdn_recurrent(const GaGdnParams* g, void* stream) {
+  int dev;
+  if (current_device(&dev)) return 1;
+  if (!g) return fail("null params");
+  if (g->k_dim != ga::gdn::KD || g->v_dim != ga::gdn::VD) return fail("k_dim/v_dim must be 128");
+  if (g->h <= 0 || g->hv <= 0 || g->hv % g->h) return fail("hv %d must be a multiple of h %d", g->hv, g->h);
+  if (g->tokens < 1 || g->tokens > 8) return fail("tokens %d outside 1..8", g->tokens);
+  if (g->batch <= 0) return fail("batch %d", g->batch);
+  if (!g->q || !g->k || !g->v || !g->a || !g->b || !g->A_log || !g->dt_bias || !g->state || !g->cache_indices || !g->out)
+    return fail("null tensor pointer");
+  if (reinterpret_cast<uintptr_t>(g->state) % 16 || g->state_stride_slot % 4) return fail("state must be 16-byte aligned");
+  ga::gdn::GdnDev d;
+  std::memset(&d, 0, sizeof(d));
+  d.q = static_cast<const __nv_bfloat16*>(g->q);
+  d.k = static_cast<const __nv_bfloat16*>(g->k);
+  d.v = static_cast<const __nv_bfloat16*>(g->v);
+  d.q_sn = g->q_stride_seq, d.q_st = g->q_stride_tok;
+  d.k_sn = g->k_stride_seq, d.k_st = g->k_stride_tok;
+  d.v_sn = g->v_stride_seq, d.v_st = g->v_stride_tok;
+  d.a = static_cast<const __nv_bfloat16*>(g->a);
+  d.b = static_cast<const __nv_bfloat16*>(g->b);
+  d.a_sn = g->a_stride_seq, d.a_st = g->a_stride_tok, d.b_sn = g->b_stride_seq, d.b_st = g->b_stride_tok;
+  d.A_log = g->A_log;
+  d.dt_bias = g->dt_bias;
+  d.dt_bias_bf16 = g->dt_bias_is_bf16;
+  d.state = g->state;
+  d.state_slot = g->state_stride_slot;
+  d.idx = g->cache_indices;
+  d.idx_i64 = g->cache_indices_is_i64;
+  d.accept = g->accept_lens;
+  d.qsl = g->query_start_loc;
+  d.out = g->out;
+  d.out_f32 = g->out_is_f32;
+  d.o_sn = g->o_stride_seq, d.o_st = g->o_stride_tok;
+  d.batch = g->batch, d.tokens = g->tokens, d.h = g->h, d.hv = g->hv;
+  d.l2norm = g->l2norm_qk, d.round_beta = g->round_beta_bf16, d.pad_reads_zero = g->pad_reads_zero;
+  d.scale = g->scale;
+  const long long blocks = static_cast<long long>(g->batch) * g->hv;
+  if (blocks > 0x7fffffffLL) return fail("batch * hv too large");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool bf = g->state_is_bf16 != 0;
+  int rc;
+  if (g->tokens == 1) rc = launch_gdn<1>(d, bf, (int)blocks, st);
+  else if (g->tokens == 2) rc = launch_gdn<2>(d, bf, (int)blocks, st);
+  else if (g->tokens <= 4) rc = launch_gdn<4>(d, bf, (int)blocks, st);
+  else rc = launch_gdn<8>(d, bf, (int)blocks, st);
+  if (rc) return rc;
+  g_launches = 1;
+  return 0;
+}
+
+int ga_attn_workspace_status(const void* workspace, void* stream, int* status) {
+  if (!workspace || !status) return fail("null pointer");
+  GA_CUDA(cudaMemcpyAsync(status, workspace, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  GA_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return 0;
+}
+
+}  // extern "C"

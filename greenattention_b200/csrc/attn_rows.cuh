@@ -1,0 +1,811 @@
+// FP8 (e4m3) paged-KV attention for a block of query rows against a range of KV tiles: the kernel
+// behind decode and speculative verify (split-KV, persistent, load-balanced over the SMs) and the
+// warp-level extend path.
+//
+// Replaces the reference's SM90 decode/verify kernel (csrc/sm90/attn_decode_fp8/kernel.cuh:339-657), its
+// device split planner (kernel.cuh:142-153,207-253) and its page gather (kernel.cuh:160-195). Same math:
+// rows = (query token, q head of one kv head) packed token-major (row = token * GQA + head, kernel.cuh:6-8),
+// S = scale * k_descale * Q K^T with a bf16 Q rounded to e4m3 (kernel.cuh:489-496), bottom-right causal mask
+// and optional left window (kernel.cuh:468-474,540-556), online softmax in the log2 domain with P rounded to
+// e4m3 after a x256 scale (kernel.cuh:296-336), O = v_descale * P V / l, natural-log LSE (kernel.cuh:621-653).
+//
+// B200 design (not the SM90 structure):
+//  * One persistent CTA per SM. The whole call is one stream of 64-token KV tiles ordered by (request, kv
+//    head); CTA c owns the contiguous slice [c*T/G, (c+1)*T/G) of it, so ragged contexts balance to within
+//    one tile and only the first and last unit of a slice can be partial (two workspace slots per CTA).
+//    The slice is derived on the device from the live cache_seqlens, so the grid is static under CUDA
+//    graphs (the property green_attention/attn_decode.py:28-31 asks of the split plan).
+//  * A producer warp gathers pages into a deep shared-memory ring with TMA tensor copies (128B swizzle,
+//    one box per page and 128-byte head slice; never multicast), or with 16-byte cp.async for pages too
+//    small for a swizzle-aligned box. Consumer warps read operands with ldmatrix straight from the swizzled
+//    tiles: K as the col-major B operand of e4m3 mma.sync, V through ldmatrix.trans + byte permutes.
+//  * Consumer warps are arranged MT (16-row tiles) x WN (tile groups); each group keeps its own running
+//    (max, sum, O) and the groups are merged in a fixed order at the end of a unit, so results are
+//    bit-reproducible run to run.
+#pragma once
+
+#include "ga_common.cuh"
+
+namespace ga {
+namespace attn {
+
+constexpr int TN = 64;                 // tokens per ring stage
+constexpr int ATOM_BYTES = TN * 128;   // one 128-byte-wide swizzled slab of a tile
+constexpr int SMEM_OPTIN = 232448;     // 227 KiB
+constexpr int MAX_ROWS = 128;
+constexpr float P_SHIFT = 8.f;         // P is scaled by 2^8 before the e4m3 rounding
+
+struct AttnDev {
+  const uint8_t* q;
+  int q_bf16;
+  long long q_s0, q_s1;  // elements
+  const uint8_t* k;
+  const uint8_t* v;
+  long long k_s0, k_s1, k_s2;  // page, token, head strides (bytes)
+  long long v_s0, v_s1, v_s2;
+  int page_shift, page_mask, num_pages;
+  int kvh, gqa;
+  const int* pt;
+  long long pt_s0, pt_s1;
+  const int* seqlens;
+  const int* cu;
+  const float* kd;
+  long long kd_s0, kd_s1;
+  const float* vd;
+  long long vd_s0, vd_s1;
+  void* out;
+  int out_f32;
+  long long o_s0, o_s1;
+  float* lse;
+  long long total_q;
+  int batch;
+  int window_left;
+  float scale_log2;  // softmax_scale * log2(e)
+  int use_tma;
+  int box_tok;       // tokens per TMA box = min(page_size, TN)
+  int max_q;         // decode/verify: query tokens per request are capped here (rows <= 16*MT)
+  int bq;            // extend: query tokens per row block
+  // split-KV workspace
+  int* status;
+  int* prefix;       // [batch + 1] exclusive prefix of per-request tile counts (written by CTA 0)
+  float* ws_o;       // [2*grid][16*MT][HD] normalised partial outputs
+  float* ws_lse;     // [2*grid][16*MT] log2-domain LSE of each partial
+};
+
+// Per-request tile bookkeeping shared by the main kernel and the combine kernel.
+struct SeqInfo {
+  int L, ql, tlo, cnt;
+};
+__device__ __forceinline__ SeqInfo seq_info(const AttnDev& p, int b) {
+  SeqInfo s;
+  s.L = p.seqlens[b];
+  int ql = p.cu[b + 1] - p.cu[b];
+  s.ql = ql < p.max_q ? ql : p.max_q;
+  if (s.L <= 0 || s.ql <= 0) {
+    s.tlo = 0;
+    s.cnt = 0;
+    return s;
+  }
+  int thi = (s.L + TN - 1) / TN;
+  int lower = 0;
+  if (p.window_left >= 0) {
+    lower = s.L - s.ql - p.window_left;
+    if (lower < 0) lower = 0;
+  }
+  s.tlo = lower / TN;
+  s.cnt = thi - s.tlo;
+  return s;
+}
+
+__device__ __forceinline__ int warp_incl_scan(int v, int lane) {
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    int o = __shfl_up_sync(0xffffffffu, v, d);
+    if (lane >= d) v += o;
+  }
+  return v;
+}
+
+// First tile of CTA c's slice of T tiles over G CTAs.
+__device__ __forceinline__ long long slice_start(long long T, int G, int c) { return (T * c) / G; }
+
+struct Seg {
+  int b, h;
+  int q0, nq;      // first query token (row of q) and token count of the row block
+  int pos0;        // absolute position of query token 0 of the block
+  int L;
+  int t_lo, t_hi;  // KV tiles [t_lo, t_hi) to process
+  int slot;        // < 0: the block's final result; >= 0: partial into workspace slot
+};
+
+// Walks the units (request, kv head) of one CTA's slice. Every warp of the CTA runs an identical copy.
+struct SliceWalker {
+  long long g0, g1, u0;
+  int b, h, cnt, tlo, L, ql;
+  int cta;
+  bool live;
+
+  __device__ void init(const AttnDev& p, int cta_, int G, int lane) {
+    cta = cta_;
+    long long sum = 0;
+    for (int b0 = 0; b0 < p.batch; b0 += 32) {
+      int bb = b0 + lane;
+      sum += bb < p.batch ? seq_info(p, bb).cnt : 0;
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    long long T = sum * p.kvh;
+    g0 = slice_start(T, G, cta);
+    g1 = slice_start(T, G, cta + 1);
+    live = g1 > g0;
+    if (!live) return;
+    long long pre = 0;
+    b = -1;
+    for (int b0 = 0; b0 < p.batch && b < 0; b0 += 32) {
+      int bb = b0 + lane;
+      int c = bb < p.batch ? seq_info(p, bb).cnt : 0;
+      int incl = warp_incl_scan(c, lane);
+      unsigned hit = __ballot_sync(0xffffffffu, (pre + incl) * p.kvh > g0);
+      if (hit) {
+        int src = __ffs(hit) - 1;
+        int incl_s = __shfl_sync(0xffffffffu, incl, src);
+        int c_s = __shfl_sync(0xffffffffu, c, src);
+        b = b0 + src;
+        pre += incl_s - c_s;
+      } else {
+        pre += __shfl_sync(0xffffffffu, incl, 31);
+      }
+    }
+    if (b < 0) {
+      live = false;
+      return;
+    }
+    load(p);
+    h = static_cast<int>((g0 - pre * p.kvh) / cnt);
+    u0 = pre * p.kvh + static_cast<long long>(h) * cnt;
+  }
+  __device__ void load(const AttnDev& p) {
+    SeqInfo s = seq_info(p, b);
+    cnt = s.cnt;
+    tlo = s.tlo;
+    L = s.L;
+    ql = s.ql;
+  }
+  __device__ bool next(const AttnDev& p, Seg& s) {
+    if (!live) return false;
+    long long lo = u0 > g0 ? u0 : g0;
+    long long u1 = u0 + cnt;
+    long long hi = u1 < g1 ? u1 : g1;
+    s.b = b;
+    s.h = h;
+    s.q0 = p.cu[b];
+    s.nq = ql;
+    s.pos0 = L - ql;
+    s.L = L;
+    s.t_lo = tlo + static_cast<int>(lo - u0);
+    s.t_hi = tlo + static_cast<int>(hi - u0);
+    s.slot = (lo == u0 && hi == u1) ? -1 : 2 * cta + (u0 <= g0 ? 0 : 1);
+    // advance
+    u0 = u1;
+    if (u0 >= g1) {
+      live = false;
+    } else if (++h == p.kvh) {
+      h = 0;
+      do {
+        ++b;
+        if (b >= p.batch) {
+          live = false;
+          break;
+        }
+        load(p);
+      } while (cnt == 0);
+    }
+    return true;
+  }
+};
+
+template <int HD, int MT, int WN>
+struct Cfg {
+  static constexpr int ATOMS = HD / 128;
+  static constexpr int NCW = MT * WN;               // consumer warps
+  static constexpr int THREADS = (NCW + 1) * 32;    // + one producer warp
+  static constexpr int ROWS = MT * 16;
+  static constexpr int STAGE_BYTES = 2 * ATOMS * ATOM_BYTES;  // K slabs then V slabs
+  static constexpr int V_OFF = ATOMS * ATOM_BYTES;
+  static constexpr int PITCH = HD + 4;              // floats per row of the merge buffer
+  static constexpr int MERGE_BYTES = WN > 1 ? ROWS * PITCH * 4 + ROWS * 8 : 0;
+  static constexpr int TAIL_BYTES = 1024;           // barriers
+  static constexpr int NST_RAW = (SMEM_OPTIN - 1024 - MERGE_BYTES - TAIL_BYTES) / STAGE_BYTES;
+  static constexpr int NST = NST_RAW > 16 ? 16 : NST_RAW;
+  static constexpr int SMEM_BYTES = 1024 + NST * STAGE_BYTES + MERGE_BYTES + TAIL_BYTES;
+  static_assert(HD == 128 || HD == 256, "head_dim");
+  static_assert(NST >= 3, "ring too shallow");
+};
+
+// ---------------------------------------------------------------------------------------------------
+// Producer: one warp, gathers the KV tiles of every segment into the ring.
+template <class C>
+__device__ __forceinline__ bool produce_tile(const AttnDev& p, const CUtensorMap* kmap, const CUtensorMap* vmap,
+                                             const Seg& s, int tt, uint32_t stage_addr, uint32_t full_bar, int lane) {
+  const int n0 = tt * TN;
+  bool ok = true;
+  if (p.use_tma) {
+    const int nbox = TN / p.box_tok;
+    int valid = 0;  // boxes that hold at least one live token
+    for (int i = 0; i < nbox; ++i) valid += (n0 + i * p.box_tok) < s.L;
+    if (lane == 0) mbar_expect_tx(full_bar, static_cast<uint32_t>(valid) * p.box_tok * 128 * C::ATOMS * 2);
+    __syncwarp();
+    const int items = valid * C::ATOMS * 2;
+    for (int it = lane; it < items; it += 32) {
+      int i = it / (C::ATOMS * 2);
+      int rem = it - i * (C::ATOMS * 2);
+      int is_v = rem / C::ATOMS;
+      int atom = rem - is_v * C::ATOMS;
+      int n = n0 + i * p.box_tok;
+      int page = p.pt[s.b * p.pt_s0 + (n >> p.page_shift) * p.pt_s1];
+      if (page < 0 || page >= p.num_pages) {
+        atomicExch(p.status, GA_ST_BAD_PAGE);  // recorded; the copy of an out-of-range box reads as zeros
+        ok = false;
+      }
+      uint32_t dst = stage_addr + (is_v ? C::V_OFF : 0) + atom * ATOM_BYTES + i * p.box_tok * 128;
+      tma_load_4d(dst, is_v ? vmap : kmap, full_bar, atom * 128, s.h, n & p.page_mask, page);
+    }
+  } else {
+    for (int r = lane; r < TN; r += 32) {
+      int n = n0 + r;
+      if (n < s.L) {
+        int page = p.pt[s.b * p.pt_s0 + (n >> p.page_shift) * p.pt_s1];
+        if (page < 0 || page >= p.num_pages) {
+          atomicExch(p.status, GA_ST_BAD_PAGE);
+          page = 0;
+          ok = false;
+        }
+        const uint8_t* ksrc = p.k + page * p.k_s0 + (n & p.page_mask) * p.k_s1 + s.h * p.k_s2;
+        const uint8_t* vsrc = p.v + page * p.v_s0 + (n & p.page_mask) * p.v_s1 + s.h * p.v_s2;
+#pragma unroll
+        for (int c = 0; c < C::ATOMS * 8; ++c) {
+          uint32_t off = (c >> 3) * ATOM_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+          cp_async_16(stage_addr + off, ksrc + c * 16);
+          cp_async_16(stage_addr + C::V_OFF + off, vsrc + c * 16);
+        }
+      }
+    }
+    cp_async_mbar_arrive_noinc(full_bar);
+  }
+  return ok;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Consumer state of one warp: 16 query rows (g and g+8 per lane) x HD output dims.
+template <class C>
+struct RowAcc {
+  float o[C::ATOMS * 16][4];  // [16-dim block * 2 + (even|odd dims)][c0..c3]
+  float m[2], l[2];
+  __device__ __forceinline__ void reset() {
+#pragma unroll
+    for (int i = 0; i < C::ATOMS * 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+  }
+};
+
+template <class C>
+__device__ __forceinline__ void load_q_frags(const AttnDev& p, const Seg& s, int mt, int lane,
+                                             uint32_t (&qf)[C::ATOMS * 4][4], int (&pos)[2]) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    int r = mt * 16 + g + half * 8;
+    int tq = r / p.gqa;
+    int hq = r - tq * p.gqa;
+    bool valid = tq < s.nq;
+    pos[half] = valid ? s.pos0 + tq : -1;
+    const uint8_t* base = p.q;
+    long long off = (static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1);
+#pragma unroll
+    for (int ks = 0; ks < C::ATOMS * 4; ++ks) {
+#pragma unroll
+      for (int sub = 0; sub < 2; ++sub) {
+        int d = ks * 32 + sub * 16 + t * 4;
+        uint32_t packed = 0;
+        if (valid) {
+          if (p.q_bf16) {
+            uint2 raw = *reinterpret_cast<const uint2*>(base + (off + d) * 2);
+            packed = pack_e4m3x4(bf16_bits_to_f32(raw.x & 0xffffu), bf16_bits_to_f32(raw.x >> 16),
+                                 bf16_bits_to_f32(raw.y & 0xffffu), bf16_bits_to_f32(raw.y >> 16));
+          } else {
+            packed = *reinterpret_cast<const uint32_t*>(base + off + d);
+          }
+        }
+        qf[ks][sub * 2 + half] = packed;  // a0: row g k-lo, a1: row g+8 k-lo, a2: row g k-hi, a3: row g+8 k-hi
+      }
+    }
+  }
+}
+
+// One 64-token tile: S = Q K^T, mask, online softmax, O += P V.
+template <class C>
+__device__ __forceinline__ void consume_tile(const AttnDev& p, const Seg& s, int tt, uint32_t stage_addr,
+                                             const uint32_t (&qf)[C::ATOMS * 4][4], const int (&pos)[2],
+                                             bool hi_rows, float sl2, RowAcc<C>& acc, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = tt * TN;
+  const int lrow = lane & 7, lmat = lane >> 3;
+
+  float sc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int row = j * 8 + lrow;
+#pragma unroll
+    for (int q4 = 0; q4 < C::ATOMS * 2; ++q4) {  // 64 dims (two k-steps) per ldmatrix.x4
+      int c = q4 * 4 + lmat;                     // 16-byte chunk of the head vector
+      uint32_t addr = stage_addr + (c >> 3) * ATOM_BYTES + row * 128 + (((c & 7) ^ lrow) << 4);
+      uint32_t r0, r1, r2, r3;
+      ldsm_x4(addr, r0, r1, r2, r3);
+      mma_e4m3_16x8x32(sc[j], qf[q4 * 2], r0, r1);
+      mma_e4m3_16x8x32(sc[j], qf[q4 * 2 + 1], r2, r3);
+    }
+  }
+
+  // Mask only where the tile touches the causal diagonal, the window edge or the end of the sequence.
+  const int first_pos = s.pos0, last_pos = s.pos0 + s.nq - 1;
+  const bool need_mask = (n0 + TN > first_pos + 1) || (p.window_left >= 0 && n0 < last_pos - p.window_left);
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+  if (need_mask) {
+    const int lo0 = p.window_left >= 0 ? pos[0] - p.window_left : -(1 << 30);
+    const int lo1 = p.window_left >= 0 ? pos[1] - p.window_left : -(1 << 30);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        int col = n0 + j * 8 + t * 2 + e;
+        float a = sc[j][e] * sl2, b = sc[j][2 + e] * sl2;
+        a = (col <= pos[0] && col >= lo0) ? a : -INFINITY;
+        b = (col <= pos[1] && col >= lo1) ? b : -INFINITY;
+        sc[j][e] = a;
+        sc[j][2 + e] = b;
+        mx0 = fmaxf(mx0, a);
+        mx1 = fmaxf(mx1, b);
+      }
+    }
+    // Rows past the end of the sequence may hold stale bytes (NaN patterns): their P is exactly 0, so
+    // V must be finite there. Zero those V rows in place before they are read.
+    if (n0 + TN > s.L) {
+      int first = s.L - n0;
+      if (first < 0) first = 0;
+      for (int idx = first * (C::ATOMS * 8) + lane; idx < TN * C::ATOMS * 8; idx += 32) {
+        int row = idx / (C::ATOMS * 8), c = idx - row * (C::ATOMS * 8);
+        uint32_t a = stage_addr + C::V_OFF + (c >> 3) * ATOM_BYTES + row * 128 + ((c & 7) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
+      }
+      __syncwarp();
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        sc[j][e] *= sl2;
+        sc[j][2 + e] *= sl2;
+        mx0 = fmaxf(mx0, sc[j][e]);
+        mx1 = fmaxf(mx1, sc[j][2 + e]);
+      }
+    }
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mn0 = fmaxf(acc.m[0], mx0), mn1 = fmaxf(acc.m[1], mx1);
+  const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+  const float al0 = ex2(acc.m[0] - mu0), al1 = ex2(acc.m[1] - mu1);
+  acc.m[0] = mn0;
+  acc.m[1] = mn1;
+  if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+    acc.l[0] *= al0;
+    acc.l[1] *= al1;
+#pragma unroll
+    for (int i = 0; i < C::ATOMS * 16; ++i) {
+      acc.o[i][0] *= al0;
+      acc.o[i][1] *= al0;
+      acc.o[i][2] *= al1;
+      acc.o[i][3] *= al1;
+    }
+  }
+  const float sh0 = P_SHIFT - mu0, sh1 = P_SHIFT - mu1;
+  // P is split into two e4m3 terms, hi = P rounded to 4 significant bits and lo = P - hi, and both are
+  // multiplied with V into the same accumulators: the product then carries ~2^-8 relative error per
+  // probability instead of the 2^-4 of a single e4m3 rounding, which is what keeps short and sharply
+  // peaked rows inside the parity tolerance. The decode path is HBM-bound, the extra MMAs are free.
+  uint32_t pa[2][4], pl[2][4];
+#pragma unroll
+  for (int c2 = 0; c2 < 2; ++c2) {
+    float e[4][4], r[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      e[i][0] = ex2(sc[c2 * 4 + i][0] + sh0);
+      e[i][1] = ex2(sc[c2 * 4 + i][1] + sh0);
+      acc.l[0] += e[i][0] + e[i][1];
+      if (hi_rows) {
+        e[i][2] = ex2(sc[c2 * 4 + i][2] + sh1);
+        e[i][3] = ex2(sc[c2 * 4 + i][3] + sh1);
+        acc.l[1] += e[i][2] + e[i][3];
+      } else {
+        e[i][2] = e[i][3] = 0.f;
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float hi = __uint_as_float((__float_as_uint(e[i][c]) + 0x00080000u) & 0xfff00000u);
+        r[i][c] = e[i][c] - hi;
+        e[i][c] = hi;
+      }
+    }
+    pa[c2][0] = pack_e4m3x4(e[0][0], e[0][1], e[1][0], e[1][1]);
+    pa[c2][1] = hi_rows ? pack_e4m3x4(e[0][2], e[0][3], e[1][2], e[1][3]) : 0u;
+    pa[c2][2] = pack_e4m3x4(e[2][0], e[2][1], e[3][0], e[3][1]);
+    pa[c2][3] = hi_rows ? pack_e4m3x4(e[2][2], e[2][3], e[3][2], e[3][3]) : 0u;
+    pl[c2][0] = pack_e4m3x4(r[0][0], r[0][1], r[1][0], r[1][1]);
+    pl[c2][1] = hi_rows ? pack_e4m3x4(r[0][2], r[0][3], r[1][2], r[1][3]) : 0u;
+    pl[c2][2] = pack_e4m3x4(r[2][0], r[2][1], r[3][0], r[3][1]);
+    pl[c2][3] = hi_rows ? pack_e4m3x4(r[2][2], r[2][3], r[3][2], r[3][3]) : 0u;
+  }
+  // O += P V. ldmatrix.trans hands each lane V bytes of two tokens x two dims; one byte permute per
+  // register pair turns them into the (4 tokens, 1 dim) words of the B fragment. The token order this
+  // induces inside a 32-token chunk is the order the P fragments above already have.
+  const uint32_t vbase = stage_addr + C::V_OFF;
+#pragma unroll
+  for (int c2 = 0; c2 < 2; ++c2) {
+    const int row = (c2 * 4 + lmat) * 8 + lrow;
+#pragma unroll
+    for (int db = 0; db < C::ATOMS * 8; ++db) {
+      uint32_t addr = vbase + (db >> 3) * ATOM_BYTES + row * 128 + (((db & 7) ^ lrow) << 4);
+      uint32_t r0, r1, r2, r3;
+      ldsm_x4_trans(addr, r0, r1, r2, r3);
+      const uint32_t e0 = prmt(r0, r1, 0x6420), e1 = prmt(r2, r3, 0x6420);
+      const uint32_t o0 = prmt(r0, r1, 0x7531), o1 = prmt(r2, r3, 0x7531);
+      mma_e4m3_16x8x32(acc.o[db * 2], pa[c2], e0, e1);
+      mma_e4m3_16x8x32(acc.o[db * 2], pl[c2], e0, e1);
+      mma_e4m3_16x8x32(acc.o[db * 2 + 1], pa[c2], o0, o1);
+      mma_e4m3_16x8x32(acc.o[db * 2 + 1], pl[c2], o0, o1);
+    }
+  }
+}
+
+// Final value of one (row, 4 consecutive dims) cell, to the output tensor or to a workspace slot.
+__device__ __forceinline__ void store_cell(const AttnDev& p, const Seg& s, int hd, int rows, int r, int d,
+                                           float4 o, float inv, float vds) {
+  if (s.slot >= 0) {
+    float4 w = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+    *reinterpret_cast<float4*>(p.ws_o + (static_cast<long long>(s.slot) * rows + r) * hd + d) = w;
+    return;
+  }
+  int tq = r / p.gqa, hq = r - tq * p.gqa;
+  long long off = static_cast<long long>(s.q0 + tq) * p.o_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.o_s1 + d;
+  float f = inv * vds;
+  if (p.out_f32) {
+    *reinterpret_cast<float4*>(static_cast<float*>(p.out) + off) = make_float4(o.x * f, o.y * f, o.z * f, o.w * f);
+  } else {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * f, o.y * f);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(o.z * f, o.w * f);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out) + off) = pk;
+  }
+}
+__device__ __forceinline__ void store_lse(const AttnDev& p, const Seg& s, int rows, int r, float m, float l) {
+  float lse2 = l > 0.f ? m + lg2(l) - P_SHIFT : -INFINITY;
+  if (s.slot >= 0) {
+    p.ws_lse[static_cast<long long>(s.slot) * rows + r] = lse2;
+  } else if (p.lse != nullptr) {
+    int tq = r / p.gqa, hq = r - tq * p.gqa;
+    p.lse[static_cast<long long>(s.h * p.gqa + hq) * p.total_q + s.q0 + tq] = lse2 * 0.6931471805599453f;
+  }
+}
+
+// MODE 0: persistent split-KV over the tile stream (decode / verify). MODE 1: one row block of
+// p.bq query tokens per CTA over everything it can see (extend).
+template <int HD, int MT, int WN, int MODE>
+__global__ void __launch_bounds__(Cfg<HD, MT, WN>::THREADS, 1)
+attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
+                 const __grid_constant__ CUtensorMap vmap) {
+  using C = Cfg<HD, MT, WN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t ring = base;
+  const uint32_t merge = ring + C::NST * C::STAGE_BYTES;
+  const uint32_t bars = merge + C::MERGE_BYTES;  // full[NST], empty[NST]
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  float* mergeO = reinterpret_cast<float*>(gen_base + C::NST * C::STAGE_BYTES);
+  float* mergeM = mergeO + C::ROWS * C::PITCH;
+  float* mergeL = mergeM + C::ROWS;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::NST; ++i) {
+      mbar_init(bars + i * 8, p.use_tma ? 1 : 32);
+      mbar_init(bars + (C::NST + i) * 8, MT);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  // ---- segment source
+  SliceWalker walk;
+  Seg one;
+  bool one_pending = false;
+  if (MODE == 0) {
+    walk.init(p, blockIdx.x, gridDim.x, lane);
+    if (blockIdx.x == 0 && warp == 0) {  // publish the per-request prefix for the combine kernel
+      int pre = 0;
+      for (int b0 = 0; b0 < p.batch; b0 += 32) {
+        int bb = b0 + lane;
+        int c = bb < p.batch ? seq_info(p, bb).cnt : 0;
+        int incl = warp_incl_scan(c, lane);
+        if (bb < p.batch) p.prefix[bb] = pre + incl - c;
+        pre += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) p.prefix[p.batch] = pre;
+    }
+  } else {
+    // Row block x of the call, heaviest (latest) blocks first.
+    int total = 0, found_b = -1, found_pre = 0, pre = 0;
+    for (int b0 = 0; b0 < p.batch; b0 += 32) {
+      int bb = b0 + lane;
+      int ql = bb < p.batch ? p.cu[bb + 1] - p.cu[bb] : 0;
+      total += (ql + p.bq - 1) / p.bq;
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+    int x = total - 1 - static_cast<int>(blockIdx.x);
+    if (x >= 0) {
+      for (int b0 = 0; b0 < p.batch && found_b < 0; b0 += 32) {
+        int bb = b0 + lane;
+        int ql = bb < p.batch ? p.cu[bb + 1] - p.cu[bb] : 0;
+        int nb = (ql + p.bq - 1) / p.bq;
+        int incl = warp_incl_scan(nb, lane);
+        unsigned hit = __ballot_sync(0xffffffffu, pre + incl > x);
+        if (hit) {
+          int src = __ffs(hit) - 1;
+          found_b = b0 + src;
+          found_pre = pre + __shfl_sync(0xffffffffu, incl, src) - __shfl_sync(0xffffffffu, nb, src);
+        } else {
+          pre += __shfl_sync(0xffffffffu, incl, 31);
+        }
+      }
+    }
+    if (found_b >= 0) {
+      int b = found_b, j = x - found_pre;
+      int ql = p.cu[b + 1] - p.cu[b];
+      one.b = b;
+      one.h = blockIdx.y;
+      one.q0 = p.cu[b] + j * p.bq;
+      one.nq = min(p.bq, ql - j * p.bq);
+      one.L = p.seqlens[b];
+      one.pos0 = one.L - ql + j * p.bq;
+      int last = one.pos0 + one.nq - 1;
+      if (last > one.L - 1) last = one.L - 1;
+      one.t_hi = last >= 0 ? last / TN + 1 : 0;
+      int lower = p.window_left >= 0 ? one.pos0 - p.window_left : 0;
+      one.t_lo = lower > 0 ? lower / TN : 0;
+      if (one.t_lo > one.t_hi) one.t_lo = one.t_hi;
+      one.slot = -1;
+      one_pending = true;
+    }
+  }
+
+  Seg s;
+  int it = 0;  // tiles of this CTA so far: ring position shared by producer and consumers
+  if (warp == C::NCW) {
+    // ------------------------------------------------------------------ producer warp
+    if (p.use_tma && lane == 0) {
+      tma_prefetch_desc(&kmap);
+      tma_prefetch_desc(&vmap);
+    }
+    while (true) {
+      if (MODE == 0) {
+        if (!walk.next(p, s)) break;
+      } else {
+        if (!one_pending) break;
+        s = one;
+        one_pending = false;
+      }
+      for (int tt = s.t_lo; tt < s.t_hi; ++tt, ++it) {
+        const int stage = it % C::NST, use = it / C::NST;
+        if (use > 0 && !mbar_wait(bars + (C::NST + stage) * 8, (use - 1) & 1)) {
+          if (lane == 0) atomicExch(p.status, GA_ST_WAIT_EMPTY);
+          return;
+        }
+        produce_tile<C>(p, &kmap, &vmap, s, tt, ring + stage * C::STAGE_BYTES, bars + stage * 8, lane);
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumer warps
+  const int mt = warp % MT, wn = warp / MT;
+  const int g = lane >> 2, t = lane & 3;
+  bool failed = false;
+  RowAcc<C> acc;
+  uint32_t qf[C::ATOMS * 4][4];
+  int pos[2];
+  while (true) {
+    if (MODE == 0) {
+      if (!walk.next(p, s)) break;
+    } else {
+      if (!one_pending) break;
+      s = one;
+      one_pending = false;
+    }
+    load_q_frags<C>(p, s, mt, lane, qf, pos);
+    acc.reset();
+    const bool hi_rows = s.nq * p.gqa > mt * 16 + 8;
+    const bool any_rows = s.nq * p.gqa > mt * 16;
+    const float kds = p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f;
+    const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
+    const float sl2 = p.scale_log2 * kds;
+    for (int tt = s.t_lo; tt < s.t_hi; ++tt, ++it) {
+      if (WN > 1 && (it % WN) != wn) continue;
+      const int stage = it % C::NST, use = it / C::NST;
+      // A wait that runs out is recorded once; the warp then drains its loops without touching the
+      // ring so that it still reaches the named barriers the other consumer warps wait on.
+      if (!failed && !mbar_wait(bars + stage * 8, use & 1)) {
+        if (lane == 0) atomicExch(p.status, GA_ST_WAIT_FULL);
+        failed = true;
+      }
+      if (failed) continue;
+      if (any_rows) consume_tile<C>(p, s, tt, ring + stage * C::STAGE_BYTES, qf, pos, hi_rows, sl2, acc, lane);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + (C::NST + stage) * 8);
+    }
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      acc.l[hf] += __shfl_xor_sync(0xffffffffu, acc.l[hf], 1);
+      acc.l[hf] += __shfl_xor_sync(0xffffffffu, acc.l[hf], 2);
+    }
+    const int valid_rows = s.nq * p.gqa;
+    if (WN == 1) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        int r = mt * 16 + g + hf * 8;
+        if (r < valid_rows) {
+          float inv = acc.l[hf] > 0.f ? 1.f / acc.l[hf] : 0.f;
+#pragma unroll
+          for (int db = 0; db < C::ATOMS * 8; ++db) {
+            float4 o = make_float4(acc.o[db * 2][hf * 2], acc.o[db * 2 + 1][hf * 2], acc.o[db * 2][hf * 2 + 1],
+                                   acc.o[db * 2 + 1][hf * 2 + 1]);
+            store_cell(p, s, HD, C::ROWS, r, db * 16 + t * 4, o, inv, vds);
+          }
+          if (t == 0) store_lse(p, s, C::ROWS, r, acc.m[hf], acc.l[hf]);
+        }
+      }
+    } else {
+      // Fold the WN tile groups in a fixed order through one shared buffer.
+      for (int round = 0; round < WN; ++round) {
+        if (wn == round) {
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            int r = mt * 16 + g + hf * 8;
+            float f_old = 0.f, f_own = 1.f, m_new = acc.m[hf], l_new = acc.l[hf];
+            if (round > 0) {
+              float m_old = mergeM[r], l_old = mergeL[r];
+              m_new = fmaxf(m_old, acc.m[hf]);
+              float mu = m_new == -INFINITY ? 0.f : m_new;
+              f_old = ex2(m_old - mu);
+              f_own = ex2(acc.m[hf] - mu);
+              l_new = l_old * f_old + acc.l[hf] * f_own;
+            }
+            float* orow = mergeO + r * C::PITCH + t * 4;
+#pragma unroll
+            for (int db = 0; db < C::ATOMS * 8; ++db) {
+              float4 o = make_float4(acc.o[db * 2][hf * 2], acc.o[db * 2 + 1][hf * 2], acc.o[db * 2][hf * 2 + 1],
+                                     acc.o[db * 2 + 1][hf * 2 + 1]);
+              float4* cell = reinterpret_cast<float4*>(orow + db * 16);
+              if (round > 0) {
+                float4 old = *cell;
+                o = make_float4(old.x * f_old + o.x * f_own, old.y * f_old + o.y * f_own,
+                                old.z * f_old + o.z * f_own, old.w * f_old + o.w * f_own);
+              }
+              *cell = o;
+            }
+            __syncwarp();
+            if (t == 0) {
+              mergeM[r] = m_new;
+              mergeL[r] = l_new;
+            }
+          }
+        }
+        named_bar_sync(1, C::NCW * 32);
+      }
+      const int tid = threadIdx.x;  // consumer threads are 0 .. NCW*32-1
+      for (int idx = tid; idx < valid_rows * (HD / 4); idx += C::NCW * 32) {
+        int r = idx / (HD / 4), d = (idx - r * (HD / 4)) * 4;
+        float l = mergeL[r];
+        float inv = l > 0.f ? 1.f / l : 0.f;
+        float4 o = *reinterpret_cast<const float4*>(mergeO + r * C::PITCH + d);
+        store_cell(p, s, HD, C::ROWS, r, d, o, inv, vds);
+        if (d == 0) store_lse(p, s, C::ROWS, r, mergeM[r], l);
+      }
+      named_bar_sync(1, C::NCW * 32);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Combine: one CTA per (request, kv head). Writes zeros / -inf for requests without keys, leaves units
+// that a single CTA finished alone, and merges the partials of split units in slice order
+// (math of the reference's combine kernel, kernel.cuh:665-749; no atomics, so bit-reproducible).
+template <int HD>
+__global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant__ AttnDev p, int G, int rows_cap) {
+  const int b = blockIdx.x, h = blockIdx.y;
+  grid_dep_wait();
+  SeqInfo si = seq_info(p, b);
+  int ql_all = p.cu[b + 1] - p.cu[b];
+  if (ql_all <= 0) return;
+  const int q0 = p.cu[b];
+  const int nq = si.ql > 0 ? si.ql : (ql_all < p.max_q ? ql_all : p.max_q);
+  const int rows = nq * p.gqa;
+  const float vds = p.vd ? p.vd[b * p.vd_s0 + h * p.vd_s1] : 1.f;
+  Seg s;
+  s.h = h;
+  s.q0 = q0;
+  s.slot = -1;
+  if (si.cnt == 0) {
+    for (int idx = threadIdx.x; idx < rows * (HD / 4); idx += blockDim.x) {
+      int r = idx / (HD / 4), d = (idx - r * (HD / 4)) * 4;
+      store_cell(p, s, HD, rows_cap, r, d, make_float4(0.f, 0.f, 0.f, 0.f), 0.f, vds);
+      if (d == 0) store_lse(p, s, rows_cap, r, -INFINITY, 0.f);
+    }
+    return;
+  }
+  const long long T = static_cast<long long>(p.prefix[p.batch]) * p.kvh;
+  const long long u0 = static_cast<long long>(p.prefix[b]) * p.kvh + static_cast<long long>(h) * si.cnt;
+  const long long u1 = u0 + si.cnt;
+  auto cta_of = [&](long long x) {
+    long long c = ((x + 1) * G - 1) / T;
+    if (c > G - 1) c = G - 1;
+    if (c < 0) c = 0;
+    while (c > 0 && slice_start(T, G, static_cast<int>(c)) > x) --c;
+    while (c < G - 1 && slice_start(T, G, static_cast<int>(c) + 1) <= x) ++c;
+    return static_cast<int>(c);
+  };
+  const int c0 = cta_of(u0), c1 = cta_of(u1 - 1);
+  if (c0 == c1) return;
+  const int slot0 = 2 * c0 + (u0 <= slice_start(T, G, c0) ? 0 : 1);
+  for (int idx = threadIdx.x; idx < rows * (HD / 4); idx += blockDim.x) {
+    int r = idx / (HD / 4), d = (idx - r * (HD / 4)) * 4;
+    float mx = -INFINITY;
+    for (int c = c0; c <= c1; ++c) {
+      if (slice_start(T, G, c + 1) == slice_start(T, G, c)) continue;  // a CTA with an empty slice wrote nothing
+      int slot = c == c0 ? slot0 : 2 * c;
+      mx = fmaxf(mx, __ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + r));
+    }
+    float den = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (mx != -INFINITY) {
+      for (int c = c0; c <= c1; ++c) {
+        if (slice_start(T, G, c + 1) == slice_start(T, G, c)) continue;
+        int slot = c == c0 ? slot0 : 2 * c;
+        float w = ex2(__ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + r) - mx);
+        float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (static_cast<long long>(slot) * rows_cap + r) * HD + d));
+        den += w;
+        o.x += w * v.x;
+        o.y += w * v.y;
+        o.z += w * v.z;
+        o.w += w * v.w;
+      }
+    }
+    float inv = den > 0.f ? 1.f / den : 0.f;
+    store_cell(p, s, HD, rows_cap, r, d, o, inv, vds);
+    if (d == 0) {
+      // store_lse expects (m, l) with l carrying the 2^P_SHIFT factor of the main kernel
+      store_lse(p, s, rows_cap, r, mx, den * exp2f(P_SHIFT));
+    }
+  }
+}
+
+}  // namespace attn
+}  // namespace ga
