@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib", "lib
 ABI_VERSION = 1
 
 EXPORTS = (
-    "ga_init", "ga_attn_workspace_bytes", "ga_attn_decode", "ga_attn_extend", "ga_attn_merge",
+    "ga_init", "ga_attn_workspace_bytes", "ga_attn_decode", "ga_attn_extend", "ga_attn_decode_noalloc", "ga_attn_merge",
     "ga_gdn_recurrent", "ga_last_launch_count", "ga_attn_workspace_status", "ga_last_error",
     "ga_abi_version", "ga_sm_count",
 )
@@ -93,6 +93,7 @@ def lib() -> ctypes.CDLL:
         handle.ga_attn_workspace_bytes.argtypes = [c_int, c_int]
         handle.ga_attn_workspace_bytes.restype = c_size_t
         for name, ptype in (("ga_attn_decode", GaAttnParams), ("ga_attn_extend", GaAttnParams),
+                            ("ga_attn_decode_noalloc", GaAttnParams),
                             ("ga_attn_merge", GaMergeParams), ("ga_gdn_recurrent", GaGdnParams)):
             fn = getattr(handle, name)
             fn.argtypes = [POINTER(ptype), c_void_p]

@@ -291,9 +291,22 @@ def _run(
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     stream = torch.cuda.current_stream(dev).cuda_stream
     lib = _C.lib()
-    fn = lib.ga_attn_decode if kind == "decode" else lib.ga_attn_extend
+    fn = {"decode": lib.ga_attn_decode, "extend": lib.ga_attn_extend,
+          "decode_noalloc": lib.ga_attn_decode_noalloc}[kind]
     _C.check(fn(ctypes.byref(p), stream), f"ga_attn_{kind}")
     return (out, lse) if return_softmax_lse else out
+
+
+def decode_noalloc(**kw):
+    """Decode / verify through ``ga_attn_decode_noalloc``: the variant for hosts that cannot hand the library a
+    workspace (no device allocator of their own, or allocation banned after start-up). Same arguments and
+    result as the launcher ``select`` returns, within that entry point's limits (batch <= 1024, GQA * query
+    tokens <= 16); larger calls raise. Calls on one device share a built-in scratch array and must not overlap."""
+    fn = select(kw)
+    if not callable(fn):
+        raise dispatch.Declined(f"decode_noalloc: {fn}")
+    wl = _window_left(kw)
+    return _run("decode_noalloc", window_left=wl, **{k: v for k, v in kw.items() if k != "window_size"})
 
 
 def decode_partial(**kw):

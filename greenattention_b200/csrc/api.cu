@@ -311,6 +311,66 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
   return 0;
 }
 
+// ---- decode without a caller-provided workspace -------------------------------------------------
+// Scratch for ga_attn_decode_noalloc: lives in the library image, one copy per GPU that loads the
+// library, held until the process exits. Sized for the limits below and nothing larger.
+constexpr int kNoAllocMaxBatch = 1024;   // requests per call
+constexpr int kNoAllocMaxSm = 160;       // CTAs of the persistent grid (one per SM)
+constexpr int kNoAllocRows = 16;         // max_seqlen_q * (q_heads / kv_heads) per (request, kv head)
+constexpr size_t kNoAllocPrefixBytes = ((kNoAllocMaxBatch + 1) * 4 + 255) / 256 * 256;
+constexpr size_t kNoAllocLseBytes = static_cast<size_t>(2 * kNoAllocMaxSm) * kNoAllocRows * 4;
+constexpr size_t kNoAllocOBytes = static_cast<size_t>(2 * kNoAllocMaxSm) * kNoAllocRows * 256 * 4;
+constexpr size_t kNoAllocBytes = kWsHeader + kNoAllocPrefixBytes + kNoAllocLseBytes + kNoAllocOBytes;  // ~5.03 MiB
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+// In host code `g_noalloc_scratch` is only a handle for the symbol; the address a kernel can use is
+// looked up per device and cached here.
+static unsigned char* g_noalloc_ptr[64] = {nullptr};
+
+int ga_attn_decode_noalloc(const GaAttnParams* a, void* stream) {
+  int dev;
+  if (current_device(&dev)) return 1;
+  ga::attn::AttnDev d;
+  CUtensorMap kmap, vmap;
+  if (fill_attn(a, &d, &kmap, &vmap)) return 1;
+  const int rows = a->max_seqlen_q * d.gqa;
+  const int sm = g_dev[dev].sm_count;
+  if (a->max_seqlen_q < 1 || rows > kNoAllocRows)
+    return fail("ga_attn_decode_noalloc: max_seqlen_q %d x GQA %d = %d rows exceeds the built-in scratch (%d rows); "
+                "use ga_attn_decode with a workspace", a->max_seqlen_q, d.gqa, rows, kNoAllocRows);
+  if (a->batch > kNoAllocMaxBatch)
+    return fail("ga_attn_decode_noalloc: batch %d exceeds the built-in scratch (%d requests); use ga_attn_decode "
+                "with a workspace", a->batch, kNoAllocMaxBatch);
+  if (sm > kNoAllocMaxSm)
+    return fail("ga_attn_decode_noalloc: %d SMs exceed the built-in scratch (%d CTAs)", sm, kNoAllocMaxSm);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // First call on this device (it is the current one): resolve the device address of the array.
+    void* ptr = nullptr;
+    GA_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    if (ptr == nullptr) return fail("ga_attn_decode_noalloc: no device address for the built-in scratch");
+    g_noalloc_ptr[dev] = static_cast<unsigned char*>(ptr);
+  }
+  unsigned char* ws = g_noalloc_ptr[dev];
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left. Only the status word has to start at zero; the
+  // prefix table and the partial slots are rewritten by every call before they are read.
+  GA_CUDA(cudaMemsetAsync(ws, 0, sizeof(int), st));
+  d.status = reinterpret_cast<int*>(ws);
+  d.prefix = reinterpret_cast<int*>(ws + kWsHeader);
+  d.ws_lse = reinterpret_cast<float*>(ws + kWsHeader + kNoAllocPrefixBytes);
+  d.ws_o = reinterpret_cast<float*>(ws + kWsHeader + kNoAllocPrefixBytes + kNoAllocLseBytes);
+  d.max_q = a->max_seqlen_q;
+  d.bq = 0;
+  const AttnInstance* k = decode_instance(a->head_dim, rows);  // rows <= 16: the 16-row instance
+  k->fn<<<sm, k->threads, k->smem, st>>>(d, kmap, vmap);
+  GA_CUDA(cudaGetLastError());
+  dim3 cgrid(a->batch, a->kv_heads);
+  if (a->head_dim == 128) ga::attn::attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(d, sm, k->rows);
+  else ga::attn::attn_combine_kernel<256><<<cgrid, 128, 0, st>>>(d, sm, k->rows);
+  GA_CUDA(cudaGetLastError());
+  g_launches = 2;
+  return 0;
+}
+
 int ga_attn_extend(const GaAttnParams* a, void* stream) {
   int dev;
   if (current_device(&dev)) return 1;

@@ -116,6 +116,25 @@ size_t ga_attn_workspace_bytes(int device, int max_batch);
 
 int ga_attn_decode(const GaAttnParams* p, void* stream);
 int ga_attn_extend(const GaAttnParams* p, void* stream);
+
+/* Decode / verify for hosts that cannot give the library a workspace. No counterpart in the reference
+ * (there Python always allocates the split workspace: green_attention/attn_decode.py:109-115).
+ *
+ * Same call and same result as ga_attn_decode, but `workspace` / `workspace_bytes` are ignored: the split-KV
+ * scratch is a fixed array inside the library image (about 5 MiB, resident on every GPU that loads the library
+ * until the process exits). It is meant for callers that own no device allocator or may not use one where
+ * they call from: an engine that handed all free HBM to its KV pool at start-up, a latency-critical loop that
+ * bans allocation after warm-up, or a thin C / Go / Rust host that links this library and nothing else. The
+ * function itself calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs are
+ * still the caller's.
+ * Limits (larger calls are rejected with an error, use ga_attn_decode for them): batch <= 1024,
+ * max_seqlen_q * (q_heads / kv_heads) <= 16 rows, at most 160 SMs.
+ * The first call on each device looks up the device address of the array (that device must be current, as
+ * for every call); make that first call before any stream capture. All calls on a device share the one
+ * array and it keeps the previous call's contents (the status word is cleared on the stream at every call,
+ * everything else is rewritten before it is read), so two calls that may overlap on the GPU (different
+ * streams, or different host threads without ordering) race: serialise them. */
+int ga_attn_decode_noalloc(const GaAttnParams* p, void* stream);
 int ga_attn_merge(const GaMergeParams* p, void* stream);
 int ga_gdn_recurrent(const GaGdnParams* p, void* stream);
 
