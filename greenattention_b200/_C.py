@@ -34,7 +34,7 @@ class GaAttnParams(ctypes.Structure):
         ("v_stride_page", c_int64), ("v_stride_tok", c_int64), ("v_stride_head", c_int64),
         ("num_pages", c_int32), ("page_size", c_int32),
         ("q_heads", c_int32), ("kv_heads", c_int32), ("head_dim", c_int32),
-        ("page_table", c_void_p), ("pt_stride_row", c_int64), ("pt_stride_col", c_int64),
+        ("page_table", c_void_p), ("pt_stride_row", c_int64), ("pt_stride_col", c_int64), ("pt_cols", c_int32),
         ("cache_seqlens", c_void_p), ("cu_seqlens_q", c_void_p),
         ("k_descale", c_void_p), ("kd_stride_b", c_int64), ("kd_stride_h", c_int64),
         ("v_descale", c_void_p), ("vd_stride_b", c_int64), ("vd_stride_h", c_int64),

@@ -270,6 +270,7 @@ def _run(
     p.q_heads, p.kv_heads, p.head_dim = qh, k_cache.shape[2], hd
     p.page_table = page_table.data_ptr()
     p.pt_stride_row, p.pt_stride_col = page_table.stride(0), page_table.stride(1)
+    p.pt_cols = page_table.shape[1]
     p.cache_seqlens, p.cu_seqlens_q = cache_seqlens.data_ptr(), cu_seqlens_q.data_ptr()
     if k_descale is not None:
         p.k_descale = k_descale.data_ptr()

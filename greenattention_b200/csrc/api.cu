@@ -8,6 +8,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -78,7 +79,7 @@ int get_map(const MapKey& key, CUtensorMap* out) {
   e.key = key;
   CUresult r = g_encode(&e.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(key.base), dims, strides, box,
                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        getenv("GA_EXP_L2") ? (CUtensorMapL2promotion)atoi(getenv("GA_EXP_L2")) : CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code %d", (int)r);
   if (g_maps.size() >= 32) g_maps.erase(g_maps.begin());
   g_maps.push_back(e);
@@ -93,24 +94,33 @@ struct AttnInstance {
   int threads, smem, rows;
 };
 
-template <int HD, int MT, int WN, int MODE>
+template <int HD, int MT, int WN, int NP, int MODE, bool HALF = false>
 AttnInstance make_instance() {
-  using C = ga::attn::Cfg<HD, MT, WN>;
-  return {ga::attn::attn_rows_kernel<HD, MT, WN, MODE>, C::THREADS, C::SMEM_BYTES, C::ROWS};
+  using C = ga::attn::Cfg<HD, MT, WN, NP>;
+  return {ga::attn::attn_rows_kernel<HD, MT, WN, NP, MODE, HALF>, C::THREADS, C::SMEM_BYTES, C::ROWS};
 }
 
-// Row capacity 16/32/64/128 per (request, kv head) for decode / verify; extend always uses 128 rows.
+// Row capacity 8/16/32/64/128 per (request, kv head) for decode / verify; extend always uses 128 rows.
+// Warps per CTA are chosen against the register file (16K registers per SM sub-partition): up to 8 warps
+// may use 255 registers each, up to 12 warps 168.
 const AttnInstance* decode_instance(int hd, int rows) {
-  static const AttnInstance t128[4] = {make_instance<128, 1, 4, 0>(), make_instance<128, 2, 2, 0>(),
-                                       make_instance<128, 4, 1, 0>(), make_instance<128, 8, 1, 0>()};
-  static const AttnInstance t256[4] = {make_instance<256, 1, 4, 0>(), make_instance<256, 2, 2, 0>(),
-                                       make_instance<256, 4, 1, 0>(), make_instance<256, 8, 1, 0>()};
-  int i = rows <= 16 ? 0 : rows <= 32 ? 1 : rows <= 64 ? 2 : 3;
+  static const AttnInstance t128[5] = {make_instance<128, 1, 4, 4, 0, true>(), make_instance<128, 1, 4, 4, 0>(),
+                                       make_instance<128, 2, 2, 4, 0>(), make_instance<128, 4, 1, 4, 0>(),
+                                       make_instance<128, 8, 1, 4, 0>()};
+  static const AttnInstance t256[5] = {make_instance<256, 1, 4, 2, 0, true>(), make_instance<256, 1, 4, 2, 0>(),
+                                       make_instance<256, 2, 2, 2, 0>(), make_instance<256, 4, 1, 2, 0>(),
+                                       make_instance<256, 8, 1, 2, 0>()};
+  int i = rows <= 8 ? 0 : rows <= 16 ? 1 : rows <= 32 ? 2 : rows <= 64 ? 3 : 4;
+  static const AttnInstance altb = make_instance<128, 1, 6, 3, 0, true>();
+  static const AttnInstance altc = make_instance<128, 1, 8, 4, 0, true>();
+  static const AttnInstance altd = make_instance<128, 1, 6, 6, 0, true>();
+  static const char* exp = getenv("GA_EXP_WARPS");
+  if (hd == 128 && i == 0 && exp) return exp[0] == 'b' ? &altb : exp[0] == 'c' ? &altc : &altd;
   return hd == 128 ? &t128[i] : &t256[i];
 }
 const AttnInstance* extend_instance(int hd) {
-  static const AttnInstance e128 = make_instance<128, 8, 1, 1>();
-  static const AttnInstance e256 = make_instance<256, 8, 1, 1>();
+  static const AttnInstance e128 = make_instance<128, 8, 1, 4, 1>();
+  static const AttnInstance e256 = make_instance<256, 8, 1, 2, 1>();
   return hd == 128 ? &e128 : &e256;
 }
 
@@ -173,6 +183,8 @@ int fill_attn(const GaAttnParams* a, ga::attn::AttnDev* d, CUtensorMap* kmap, CU
   d->pt = a->page_table;
   d->pt_s0 = a->pt_stride_row;
   d->pt_s1 = a->pt_stride_col;
+  d->pt_cols = a->pt_cols;
+  { static const char* e = getenv("GA_EXP_DBG"); d->dbg = e ? atoi(e) : 0; }
   d->seqlens = a->cache_seqlens;
   d->cu = a->cu_seqlens_q;
   d->kd = a->k_descale, d->kd_s0 = a->kd_stride_b, d->kd_s1 = a->kd_stride_h;
@@ -258,8 +270,15 @@ int ga_init(int device) {
     g_encode = reinterpret_cast<EncodeTiledFn>(fn);
   }
   for (int hd : {128, 256}) {
-    for (int rows : {16, 32, 64, 128})
+    for (int rows : {8, 16, 32, 64, 128})
       if (set_smem(*decode_instance(hd, rows))) return 1;
+    if (hd == 128) {
+      for (const char* e : {"b", "c", "d"}) {
+        setenv("GA_EXP_WARPS", e, 1);
+        if (set_smem(*decode_instance(128, 8))) return 1;
+      }
+      unsetenv("GA_EXP_WARPS");
+    }
     if (set_smem(*extend_instance(hd))) return 1;
   }
   GA_CUDA(cudaSetDevice(prev));

@@ -47,6 +47,7 @@ struct AttnDev {
   int kvh, gqa;
   const int* pt;
   long long pt_s0, pt_s1;
+  int pt_cols;       // entries per page-table row
   const int* seqlens;
   const int* cu;
   const float* kd;
@@ -65,6 +66,7 @@ struct AttnDev {
   int box_tok;       // tokens per TMA box = min(page_size, TN)
   int max_q;         // decode/verify: query tokens per request are capped here (rows <= 16*MT)
   int bq;            // extend: query tokens per row block
+  int dbg;
   // split-KV workspace
   int* status;
   int* prefix;       // [batch + 1] exclusive prefix of per-request tile counts (written by CTA 0)
@@ -204,11 +206,16 @@ struct SliceWalker {
   }
 };
 
-template <int HD, int MT, int WN>
+constexpr int gcd_(int a, int b) { return b == 0 ? a : gcd_(b, a % b); }
+
+template <int HD, int MT, int WN, int NP_ = 4>
 struct Cfg {
   static constexpr int ATOMS = HD / 128;
   static constexpr int NCW = MT * WN;               // consumer warps
-  static constexpr int THREADS = (NCW + 1) * 32;    // + one producer warp
+  // Producer warps: each issues every NP-th tile. One warp's issue loop (barrier wait, expect_tx, TMA
+  // issue) takes on the order of a thousand cycles per tile, far too slow to keep HBM busy on its own.
+  static constexpr int NP = NP_;
+  static constexpr int THREADS = (NCW + NP) * 32;
   static constexpr int ROWS = MT * 16;
   static constexpr int STAGE_BYTES = 2 * ATOMS * ATOM_BYTES;  // K slabs then V slabs
   static constexpr int V_OFF = ATOMS * ATOM_BYTES;
@@ -216,17 +223,48 @@ struct Cfg {
   static constexpr int MERGE_BYTES = WN > 1 ? ROWS * PITCH * 4 + ROWS * 8 : 0;
   static constexpr int TAIL_BYTES = 1024;           // barriers
   static constexpr int NST_RAW = (SMEM_OPTIN - 1024 - MERGE_BYTES - TAIL_BYTES) / STAGE_BYTES;
-  static constexpr int NST = NST_RAW > 16 ? 16 : NST_RAW;
+  // The ring depth is a multiple of both WN and NP, so a stage is always filled by the same producer warp
+  // and always drained by the same consumer group. That is what makes the parity waits sound: a warp that
+  // waits for use u of a stage has itself gone through use u-1, so the barrier can never be a whole phase
+  // behind the waiter (a parity wait cannot tell phase u-2 from phase u).
+  static constexpr int LCM = WN * NP / gcd_(WN, NP);
+  static constexpr int NST_CAP = NST_RAW > 24 ? 24 : NST_RAW;
+  static constexpr int NST = NST_CAP / LCM * LCM;
   static constexpr int SMEM_BYTES = 1024 + NST * STAGE_BYTES + MERGE_BYTES + TAIL_BYTES;
   static_assert(HD == 128 || HD == 256, "head_dim");
-  static_assert(NST >= 3, "ring too shallow");
+  static_assert(NST >= 2 && NST >= LCM, "ring too shallow for this warp arrangement");
 };
 
 // ---------------------------------------------------------------------------------------------------
 // Producer: one warp, gathers the KV tiles of every segment into the ring.
+//
+// Page ids come from a register-resident window of the page table: each lane holds one entry of the
+// current 32-entry window and one of the next, so a tile costs a shuffle instead of a dependent global
+// load and the next window is already in flight when the current one runs out.
+struct PtWindow {
+  int b, base, cur, nxt;
+};
+__device__ __forceinline__ int pt_entry(const AttnDev& p, int b, int e) {
+  return e < p.pt_cols ? __ldg(p.pt + b * p.pt_s0 + e * p.pt_s1) : 0;
+}
+__device__ __forceinline__ int pt_lookup(const AttnDev& p, PtWindow& w, int b, int e, int lane) {
+  if (w.b != b || e < w.base || e >= w.base + 64) {
+    w.b = b;
+    w.base = e & ~31;
+    w.cur = pt_entry(p, b, w.base + lane);
+    w.nxt = pt_entry(p, b, w.base + 32 + lane);
+  } else if (e >= w.base + 32) {
+    w.base += 32;
+    w.cur = w.nxt;
+    w.nxt = pt_entry(p, b, w.base + 32 + lane);
+  }
+  return __shfl_sync(0xffffffffu, w.cur, e - w.base);
+}
+
 template <class C>
 __device__ __forceinline__ bool produce_tile(const AttnDev& p, const CUtensorMap* kmap, const CUtensorMap* vmap,
-                                             const Seg& s, int tt, uint32_t stage_addr, uint32_t full_bar, int lane) {
+                                             const Seg& s, int tt, uint32_t stage_addr, uint32_t full_bar, int lane,
+                                             PtWindow& win) {
   const int n0 = tt * TN;
   bool ok = true;
   if (p.use_tma) {
@@ -235,20 +273,18 @@ __device__ __forceinline__ bool produce_tile(const AttnDev& p, const CUtensorMap
     for (int i = 0; i < nbox; ++i) valid += (n0 + i * p.box_tok) < s.L;
     if (lane == 0) mbar_expect_tx(full_bar, static_cast<uint32_t>(valid) * p.box_tok * 128 * C::ATOMS * 2);
     __syncwarp();
-    const int items = valid * C::ATOMS * 2;
-    for (int it = lane; it < items; it += 32) {
-      int i = it / (C::ATOMS * 2);
-      int rem = it - i * (C::ATOMS * 2);
-      int is_v = rem / C::ATOMS;
-      int atom = rem - is_v * C::ATOMS;
-      int n = n0 + i * p.box_tok;
-      int page = p.pt[s.b * p.pt_s0 + (n >> p.page_shift) * p.pt_s1];
+    for (int i = 0; i < valid; ++i) {
+      const int n = n0 + i * p.box_tok;
+      int page = pt_lookup(p, win, s.b, n >> p.page_shift, lane);
       if (page < 0 || page >= p.num_pages) {
-        atomicExch(p.status, GA_ST_BAD_PAGE);  // recorded; the copy of an out-of-range box reads as zeros
+        if (lane == 0) atomicExch(p.status, GA_ST_BAD_PAGE);  // recorded; an out-of-range box reads as zeros
         ok = false;
       }
-      uint32_t dst = stage_addr + (is_v ? C::V_OFF : 0) + atom * ATOM_BYTES + i * p.box_tok * 128;
-      tma_load_4d(dst, is_v ? vmap : kmap, full_bar, atom * 128, s.h, n & p.page_mask, page);
+      if (lane < C::ATOMS * 2) {
+        const int is_v = lane / C::ATOMS, atom = lane - is_v * C::ATOMS;
+        uint32_t dst = stage_addr + (is_v ? C::V_OFF : 0) + atom * ATOM_BYTES + i * p.box_tok * 128;
+        tma_load_4d(dst, is_v ? vmap : kmap, full_bar, atom * 128, s.h, n & p.page_mask, page);
+      }
     }
   } else {
     for (int r = lane; r < TN; r += 32) {
@@ -324,11 +360,12 @@ __device__ __forceinline__ void load_q_frags(const AttnDev& p, const Seg& s, int
 }
 
 // One 64-token tile: S = Q K^T, mask, online softmax, O += P V.
-template <class C>
+template <class C, bool HALF>
 __device__ __forceinline__ void consume_tile(const AttnDev& p, const Seg& s, int tt, uint32_t stage_addr,
                                              const uint32_t (&qf)[C::ATOMS * 4][4], const int (&pos)[2],
-                                             bool hi_rows, float sl2, RowAcc<C>& acc, int lane) {
+                                             bool hi_rows_in, float sl2, RowAcc<C>& acc, int lane) {
   const int g = lane >> 2, t = lane & 3;
+  const bool hi_rows = HALF ? false : hi_rows_in;
   const int n0 = tt * TN;
   const int lrow = lane & 7, lmat = lane >> 3;
 
@@ -506,12 +543,13 @@ __device__ __forceinline__ void store_lse(const AttnDev& p, const Seg& s, int ro
 }
 
 // MODE 0: persistent split-KV over the tile stream (decode / verify). MODE 1: one row block of
-// p.bq query tokens per CTA over everything it can see (extend).
-template <int HD, int MT, int WN, int MODE>
-__global__ void __launch_bounds__(Cfg<HD, MT, WN>::THREADS, 1)
+// p.bq query tokens per CTA over everything it can see (extend). HALF: at most 8 live rows per CTA
+// (decode with GQA <= 8): rows 8..15 of the MMA tile carry no accumulators.
+template <int HD, int MT, int WN, int NP, int MODE, bool HALF>
+__global__ void __launch_bounds__(Cfg<HD, MT, WN, NP>::THREADS, 1)
 attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap) {
-  using C = Cfg<HD, MT, WN>;
+  using C = Cfg<HD, MT, WN, NP>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t ring = base;
@@ -598,8 +636,12 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
 
   Seg s;
   int it = 0;  // tiles of this CTA so far: ring position shared by producer and consumers
-  if (warp == C::NCW) {
-    // ------------------------------------------------------------------ producer warp
+  if (warp >= C::NCW) {
+    // ------------------------------------------------------------------ producer warps
+    const int pw = warp - C::NCW;
+    PtWindow win;
+    win.b = -1;
+    win.base = win.cur = win.nxt = 0;
     if (p.use_tma && lane == 0) {
       tma_prefetch_desc(&kmap);
       tma_prefetch_desc(&vmap);
@@ -613,12 +655,13 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
         one_pending = false;
       }
       for (int tt = s.t_lo; tt < s.t_hi; ++tt, ++it) {
+        if ((it % C::NP) != pw) continue;
         const int stage = it % C::NST, use = it / C::NST;
         if (use > 0 && !mbar_wait(bars + (C::NST + stage) * 8, (use - 1) & 1)) {
           if (lane == 0) atomicExch(p.status, GA_ST_WAIT_EMPTY);
           return;
         }
-        produce_tile<C>(p, &kmap, &vmap, s, tt, ring + stage * C::STAGE_BYTES, bars + stage * 8, lane);
+        produce_tile<C>(p, &kmap, &vmap, s, tt, ring + stage * C::STAGE_BYTES, bars + stage * 8, lane, win);
       }
     }
     return;
@@ -656,7 +699,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
         failed = true;
       }
       if (failed) continue;
-      if (any_rows) consume_tile<C>(p, s, tt, ring + stage * C::STAGE_BYTES, qf, pos, hi_rows, sl2, acc, lane);
+      if (any_rows && !(p.dbg & 1)) consume_tile<C, HALF>(p, s, tt, ring + stage * C::STAGE_BYTES, qf, pos, hi_rows, sl2, acc, lane);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + (C::NST + stage) * 8);

@@ -45,6 +45,7 @@ typedef struct GaAttnParams {
   int32_t q_heads, kv_heads, head_dim; /* head_dim 128 or 256; q_heads % kv_heads == 0 */
   const int32_t* page_table;    /* [batch, max_pages]; entries past ceil(len / page_size) are never read */
   int64_t pt_stride_row, pt_stride_col;
+  int32_t pt_cols;              /* max_pages: entries per page-table row */
   const int32_t* cache_seqlens; /* [batch] keys per request, new tokens included */
   const int32_t* cu_seqlens_q;  /* [batch + 1] */
   const float* k_descale;       /* [batch | 1, kv_heads] or NULL (= 1); multiplies the logits */
