@@ -542,6 +542,201 @@ __device__ __forceinline__ void store_lse(const AttnDev& p, const Seg& s, int ro
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Decode with at most 8 live rows per (request, kv head) (one query token, GQA <= 8): the shape the
+// production decode runs. S = Q K^T keeps the query rows in the M dimension (rows 8..15 are padding), but
+// O is accumulated TRANSPOSED, O^T[dims, rows] += V^T[dims, tokens] P^T[tokens, rows], so the 8 rows sit
+// exactly in the N = 8 dimension of the MMA: half the PV MMAs and half the accumulator registers of the
+// general path. The A operand V^T comes from ldmatrix.trans plus byte permutes (rows 0..7 of a 16-dim block
+// take the even dims, rows 8..15 the odd ones); the B operand P^T is, lane for lane, the S accumulator
+// fragment packed to e4m3. Loads and MMAs are written k-step-major / block-major so that consecutive MMAs
+// never depend on each other.
+template <class C>
+struct RowAcc8 {
+  float ot[C::ATOMS * 8][4];  // [16-dim block]: {even dim, row 2t}, {even, row 2t+1}, {odd, 2t}, {odd, 2t+1}
+  float m, l;                 // running max / sum of row g (identical in the four lanes of a quad)
+  __device__ __forceinline__ void reset() {
+#pragma unroll
+    for (int i = 0; i < C::ATOMS * 8; ++i) ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f;
+    m = -INFINITY;
+    l = 0.f;
+  }
+};
+
+template <class C>
+__device__ __forceinline__ void load_q_frags8(const AttnDev& p, const Seg& s, int lane,
+                                              uint32_t (&qf)[C::ATOMS * 4][2], int& pos) {
+  const int g = lane >> 2, t = lane & 3;
+  const int tq = g / p.gqa, hq = g - tq * p.gqa;
+  const bool valid = tq < s.nq;
+  pos = valid ? s.pos0 + tq : -1;
+  const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1;
+#pragma unroll
+  for (int ks = 0; ks < C::ATOMS * 4; ++ks) {
+#pragma unroll
+    for (int sub = 0; sub < 2; ++sub) {
+      const int d = ks * 32 + sub * 16 + t * 4;
+      uint32_t packed = 0;
+      if (valid) {
+        if (p.q_bf16) {
+          uint2 raw = *reinterpret_cast<const uint2*>(p.q + (off + d) * 2);
+          packed = pack_e4m3x4(bf16_bits_to_f32(raw.x & 0xffffu), bf16_bits_to_f32(raw.x >> 16),
+                               bf16_bits_to_f32(raw.y & 0xffffu), bf16_bits_to_f32(raw.y >> 16));
+        } else {
+          packed = *reinterpret_cast<const uint32_t*>(p.q + off + d);
+        }
+      }
+      qf[ks][sub] = packed;
+    }
+  }
+}
+
+template <class C>
+__device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, int tt, uint32_t stage_addr,
+                                              const uint32_t (&qf)[C::ATOMS * 4][2], int pos, float sl2,
+                                              RowAcc8<C>& acc, int lane) {
+  const int t = lane & 3;
+  const int n0 = tt * TN;
+  const int lrow = lane & 7, lmat = lane >> 3;
+  const uint32_t xr = static_cast<uint32_t>(lrow) << 4;
+
+  float sc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t kb[4][C::ATOMS * 2][4];
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const uint32_t rowaddr = stage_addr + ((half * 4 + jj) * 8 + lrow) * 128;
+#pragma unroll
+      for (int q4 = 0; q4 < C::ATOMS * 2; ++q4) {
+        const int c = q4 * 4 + lmat;
+        ldsm_x4(rowaddr + (c >> 3) * ATOM_BYTES + ((static_cast<uint32_t>(c & 7) << 4) ^ xr), kb[jj][q4][0],
+                kb[jj][q4][1], kb[jj][q4][2], kb[jj][q4][3]);
+      }
+    }
+#pragma unroll
+    for (int q4 = 0; q4 < C::ATOMS * 2; ++q4) {
+#pragma unroll
+      for (int sub = 0; sub < 2; ++sub) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          mma_e4m3_16x8x32_a(sc[half * 4 + jj], qf[q4 * 2 + sub][0], 0u, qf[q4 * 2 + sub][1], 0u,
+                             kb[jj][q4][sub * 2], kb[jj][q4][sub * 2 + 1]);
+        }
+      }
+    }
+  }
+
+  const bool need_mask = (n0 + TN > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
+  float mx = -INFINITY;
+  if (need_mask) {
+    const int lo = p.window_left >= 0 ? pos - p.window_left : -(1 << 30);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int col = n0 + j * 8 + t * 2 + e;
+        float a = sc[j][e] * sl2;
+        a = (col <= pos && col >= lo) ? a : -INFINITY;
+        sc[j][e] = a;
+        mx = fmaxf(mx, a);
+      }
+    }
+    if (n0 + TN > s.L) {  // stale rows past the end of the sequence: make V finite where P is exactly 0
+      int first = s.L - n0;
+      if (first < 0) first = 0;
+      for (int idx = first * (C::ATOMS * 8) + lane; idx < TN * C::ATOMS * 8; idx += 32) {
+        int row = idx / (C::ATOMS * 8), c = idx - row * (C::ATOMS * 8);
+        uint32_t a = stage_addr + C::V_OFF + (c >> 3) * ATOM_BYTES + row * 128 + ((c & 7) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
+      }
+      __syncwarp();
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      sc[j][0] *= sl2;
+      sc[j][1] *= sl2;
+      mx = fmaxf(mx, fmaxf(sc[j][0], sc[j][1]));
+    }
+  }
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+  const float mn = fmaxf(acc.m, mx);
+  const float mu = mn == -INFINITY ? 0.f : mn;
+  const float al = ex2(acc.m - mu);
+  acc.m = mn;
+  if (__any_sync(0xffffffffu, al != 1.f)) {
+    acc.l *= al;
+    const float a0 = __shfl_sync(0xffffffffu, al, (2 * t) * 4), a1 = __shfl_sync(0xffffffffu, al, (2 * t + 1) * 4);
+#pragma unroll
+    for (int i = 0; i < C::ATOMS * 8; ++i) {
+      acc.ot[i][0] *= a0;
+      acc.ot[i][1] *= a1;
+      acc.ot[i][2] *= a0;
+      acc.ot[i][3] *= a1;
+    }
+  }
+  // P = 2^(s - m + 8), split into two e4m3 terms (4 significant bits + residual), see the general path.
+  const float sh = P_SHIFT - mu;
+  uint32_t ph[8], pl[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float e0 = ex2(sc[j][0] + sh), e1 = ex2(sc[j][1] + sh);
+    acc.l += e0 + e1;
+    float h0 = __uint_as_float((__float_as_uint(e0) + 0x00080000u) & 0xfff00000u);
+    float h1 = __uint_as_float((__float_as_uint(e1) + 0x00080000u) & 0xfff00000u);
+    ph[j] = pack_e4m3x2(h0, h1);
+    pl[j] = pack_e4m3x2(e0 - h0, e1 - h1);
+  }
+  const uint32_t vbase = stage_addr + C::V_OFF;
+#pragma unroll
+  for (int c2 = 0; c2 < 2; ++c2) {
+    const uint32_t bh0 = ph[c2 * 4] | (ph[c2 * 4 + 1] << 16), bh1 = ph[c2 * 4 + 2] | (ph[c2 * 4 + 3] << 16);
+    const uint32_t bl0 = pl[c2 * 4] | (pl[c2 * 4 + 1] << 16), bl1 = pl[c2 * 4 + 2] | (pl[c2 * 4 + 3] << 16);
+    const uint32_t rowaddr = vbase + ((c2 * 4 + lmat) * 8 + lrow) * 128;
+#pragma unroll
+    for (int grp = 0; grp < C::ATOMS; ++grp) {  // eight 16-dim blocks at a time
+      uint32_t va[8][4];
+#pragma unroll
+      for (int d8 = 0; d8 < 8; ++d8) {
+        uint32_t r0, r1, r2, r3;
+        ldsm_x4_trans(rowaddr + grp * ATOM_BYTES + ((static_cast<uint32_t>(d8) << 4) ^ xr), r0, r1, r2, r3);
+        va[d8][0] = prmt(r0, r1, 0x6420);
+        va[d8][1] = prmt(r0, r1, 0x7531);
+        va[d8][2] = prmt(r2, r3, 0x6420);
+        va[d8][3] = prmt(r2, r3, 0x7531);
+      }
+#pragma unroll
+      for (int d8 = 0; d8 < 8; ++d8)
+        mma_e4m3_16x8x32_a(acc.ot[grp * 8 + d8], va[d8][0], va[d8][1], va[d8][2], va[d8][3], bh0, bh1);
+#pragma unroll
+      for (int d8 = 0; d8 < 8; ++d8)
+        mma_e4m3_16x8x32_a(acc.ot[grp * 8 + d8], va[d8][0], va[d8][1], va[d8][2], va[d8][3], bl0, bl1);
+    }
+  }
+}
+
+// Final value of one (row, 2 consecutive dims) cell of the 8-row path.
+__device__ __forceinline__ void store_pair(const AttnDev& p, const Seg& s, int hd, int rows, int r, int d, float v0,
+                                           float v1, float inv, float vds) {
+  if (s.slot >= 0) {
+    *reinterpret_cast<float2*>(p.ws_o + (static_cast<long long>(s.slot) * rows + r) * hd + d) =
+        make_float2(v0 * inv, v1 * inv);
+    return;
+  }
+  int tq = r / p.gqa, hq = r - tq * p.gqa;
+  long long off = static_cast<long long>(s.q0 + tq) * p.o_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.o_s1 + d;
+  float f = inv * vds;
+  if (p.out_f32) {
+    *reinterpret_cast<float2*>(static_cast<float*>(p.out) + off) = make_float2(v0 * f, v1 * f);
+  } else {
+    *reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(p.out) + off) = __floats2bfloat162_rn(v0 * f, v1 * f);
+  }
+}
+
 // MODE 0: persistent split-KV over the tile stream (decode / verify). MODE 1: one row block of
 // p.bq query tokens per CTA over everything it can see (extend). HALF: at most 8 live rows per CTA
 // (decode with GQA <= 8): rows 8..15 of the MMA tile carry no accumulators.
@@ -671,6 +866,106 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
   const int mt = warp % MT, wn = warp / MT;
   const int g = lane >> 2, t = lane & 3;
   bool failed = false;
+  if constexpr (HALF) {
+    RowAcc8<C> acc;
+    uint32_t qf[C::ATOMS * 4][2];
+    int pos;
+    while (true) {
+      if (MODE == 0) {
+        if (!walk.next(p, s)) break;
+      } else {
+        if (!one_pending) break;
+        s = one;
+        one_pending = false;
+      }
+      load_q_frags8<C>(p, s, lane, qf, pos);
+      acc.reset();
+      const float kds = p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f;
+      const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
+      const float sl2 = p.scale_log2 * kds;
+      for (int tt = s.t_lo; tt < s.t_hi; ++tt, ++it) {
+        if (WN > 1 && (it % WN) != wn) continue;
+        const int stage = it % C::NST, use = it / C::NST;
+        if (!failed && !mbar_wait(bars + stage * 8, use & 1)) {
+          if (lane == 0) atomicExch(p.status, GA_ST_WAIT_FULL);
+          failed = true;
+        }
+        if (failed) continue;
+        consume_tile8<C>(p, s, tt, ring + stage * C::STAGE_BYTES, qf, pos, sl2, acc, lane);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + (C::NST + stage) * 8);
+      }
+      acc.l += __shfl_xor_sync(0xffffffffu, acc.l, 1);
+      acc.l += __shfl_xor_sync(0xffffffffu, acc.l, 2);
+      const int valid_rows = s.nq * p.gqa;
+      // this lane's two output columns are query rows 2t and 2t+1; their statistics live in quads 2t, 2t+1
+      float m_r[2], l_r[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        m_r[e] = __shfl_sync(0xffffffffu, acc.m, (2 * t + e) * 4);
+        l_r[e] = __shfl_sync(0xffffffffu, acc.l, (2 * t + e) * 4);
+      }
+      if (WN == 1) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int r = 2 * t + e;
+          if (r < valid_rows) {
+            const float inv = l_r[e] > 0.f ? 1.f / l_r[e] : 0.f;
+#pragma unroll
+            for (int db = 0; db < C::ATOMS * 8; ++db)
+              store_pair(p, s, HD, C::ROWS, r, db * 16 + 2 * g, acc.ot[db][e], acc.ot[db][2 + e], inv, vds);
+            if (g == 0) store_lse(p, s, C::ROWS, r, m_r[e], l_r[e]);
+          }
+        }
+      } else {
+        for (int round = 0; round < WN; ++round) {
+          if (wn == round) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int r = 2 * t + e;
+              float f_old = 0.f, f_own = 1.f, m_new = m_r[e], l_new = l_r[e];
+              if (round > 0) {
+                const float m_old = mergeM[r], l_old = mergeL[r];
+                m_new = fmaxf(m_old, m_r[e]);
+                const float mu = m_new == -INFINITY ? 0.f : m_new;
+                f_old = ex2(m_old - mu);
+                f_own = ex2(m_r[e] - mu);
+                l_new = l_old * f_old + l_r[e] * f_own;
+              }
+#pragma unroll
+              for (int db = 0; db < C::ATOMS * 8; ++db) {
+                float2* cell = reinterpret_cast<float2*>(mergeO + r * C::PITCH + db * 16 + 2 * g);
+                float2 o = make_float2(acc.ot[db][e], acc.ot[db][2 + e]);
+                if (round > 0) {
+                  const float2 old = *cell;
+                  o = make_float2(old.x * f_old + o.x * f_own, old.y * f_old + o.y * f_own);
+                }
+                *cell = o;
+              }
+              __syncwarp();
+              if (g == 0) {
+                mergeM[r] = m_new;
+                mergeL[r] = l_new;
+              }
+            }
+          }
+          named_bar_sync(1, C::NCW * 32);
+        }
+        const int tid = threadIdx.x;
+        for (int idx = tid; idx < valid_rows * (HD / 4); idx += C::NCW * 32) {
+          int r = idx / (HD / 4), d = (idx - r * (HD / 4)) * 4;
+          float l = mergeL[r];
+          float inv = l > 0.f ? 1.f / l : 0.f;
+          float4 o = *reinterpret_cast<const float4*>(mergeO + r * C::PITCH + d);
+          store_cell(p, s, HD, C::ROWS, r, d, o, inv, vds);
+          if (d == 0) store_lse(p, s, C::ROWS, r, mergeM[r], l);
+        }
+        named_bar_sync(1, C::NCW * 32);
+      }
+    }
+    return;
+  }
   RowAcc<C> acc;
   uint32_t qf[C::ATOMS * 4][4];
   int pos[2];
@@ -699,7 +994,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
         failed = true;
       }
       if (failed) continue;
-      if (any_rows && !(p.dbg & 1)) consume_tile<C, HALF>(p, s, tt, ring + stage * C::STAGE_BYTES, qf, pos, hi_rows, sl2, acc, lane);
+      if (any_rows) consume_tile<C, HALF>(p, s, tt, ring + stage * C::STAGE_BYTES, qf, pos, hi_rows, sl2, acc, lane);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + (C::NST + stage) * 8);

@@ -98,15 +98,13 @@ __device__ __forceinline__ void mma_e4m3_16x8x32(float (&d)[4], const uint32_t (
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Same MMA when only rows 0..7 of the 16-row tile are live (a1 = a3 = 0): the two accumulator
-// registers of rows 8..15 are never kept, which halves the accumulator footprint of a decode warp.
-__device__ __forceinline__ void mma_e4m3_16x8x32_lo8(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0,
-                                                     uint32_t b1) {
-  float j0, j1;
+// Same MMA with the four A registers passed separately.
+__device__ __forceinline__ void mma_e4m3_16x8x32_a(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                   uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%9,%9};"
-      : "+f"(d0), "+f"(d1), "=f"(j0), "=f"(j1)
-      : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // Two floats -> two e4m3 bytes (round to nearest even, saturate to +-448); `lo` lands in the low byte.
