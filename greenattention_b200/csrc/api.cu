@@ -94,10 +94,10 @@ struct AttnInstance {
   int threads, smem, rows;
 };
 
-template <int HD, int MT, int WN, int NP, int MODE, bool HALF = false>
+template <int HD, int MT, int WN, int NP, int MODE, bool HALF = false, int CAP = 24>
 AttnInstance make_instance() {
-  using C = ga::attn::Cfg<HD, MT, WN, NP>;
-  return {ga::attn::attn_rows_kernel<HD, MT, WN, NP, MODE, HALF>, C::THREADS, C::SMEM_BYTES, C::ROWS};
+  using C = ga::attn::Cfg<HD, MT, WN, NP, CAP>;
+  return {ga::attn::attn_rows_kernel<HD, MT, WN, NP, MODE, HALF, CAP>, C::THREADS, C::SMEM_BYTES, C::ROWS};
 }
 
 // Row capacity 8/16/32/64/128 per (request, kv head) for decode / verify; extend always uses 128 rows.
@@ -111,9 +111,9 @@ const AttnInstance* decode_instance(int hd, int rows) {
                                        make_instance<256, 2, 2, 2, 0>(), make_instance<256, 4, 1, 2, 0>(),
                                        make_instance<256, 8, 1, 2, 0>()};
   int i = rows <= 8 ? 0 : rows <= 16 ? 1 : rows <= 32 ? 2 : rows <= 64 ? 3 : 4;
-  static const AttnInstance altb = make_instance<128, 1, 6, 3, 0, true>();
-  static const AttnInstance altc = make_instance<128, 1, 8, 4, 0, true>();
-  static const AttnInstance altd = make_instance<128, 1, 6, 6, 0, true>();
+  static const AttnInstance altb = make_instance<128, 1, 6, 2, 0, true>();
+  static const AttnInstance altc = make_instance<128, 1, 4, 2, 0, true>();
+  static const AttnInstance altd = make_instance<128, 1, 5, 1, 0, true>();
   static const char* exp = getenv("GA_EXP_WARPS");
   if (hd == 128 && i == 0 && exp) return exp[0] == 'b' ? &altb : exp[0] == 'c' ? &altc : &altd;
   return hd == 128 ? &t128[i] : &t256[i];

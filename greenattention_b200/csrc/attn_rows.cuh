@@ -208,7 +208,7 @@ struct SliceWalker {
 
 constexpr int gcd_(int a, int b) { return b == 0 ? a : gcd_(b, a % b); }
 
-template <int HD, int MT, int WN, int NP_ = 4>
+template <int HD, int MT, int WN, int NP_ = 4, int CAP_ = 24>
 struct Cfg {
   static constexpr int ATOMS = HD / 128;
   static constexpr int NCW = MT * WN;               // consumer warps
@@ -228,7 +228,7 @@ struct Cfg {
   // waits for use u of a stage has itself gone through use u-1, so the barrier can never be a whole phase
   // behind the waiter (a parity wait cannot tell phase u-2 from phase u).
   static constexpr int LCM = WN * NP / gcd_(WN, NP);
-  static constexpr int NST_CAP = NST_RAW > 24 ? 24 : NST_RAW;
+  static constexpr int NST_CAP = NST_RAW > CAP_ ? CAP_ : NST_RAW;
   static constexpr int NST = NST_CAP / LCM * LCM;
   static constexpr int SMEM_BYTES = 1024 + NST * STAGE_BYTES + MERGE_BYTES + TAIL_BYTES;
   static_assert(HD == 128 || HD == 256, "head_dim");
@@ -740,11 +740,11 @@ __device__ __forceinline__ void store_pair(const AttnDev& p, const Seg& s, int h
 // MODE 0: persistent split-KV over the tile stream (decode / verify). MODE 1: one row block of
 // p.bq query tokens per CTA over everything it can see (extend). HALF: at most 8 live rows per CTA
 // (decode with GQA <= 8): rows 8..15 of the MMA tile carry no accumulators.
-template <int HD, int MT, int WN, int NP, int MODE, bool HALF>
-__global__ void __launch_bounds__(Cfg<HD, MT, WN, NP>::THREADS, 1)
+template <int HD, int MT, int WN, int NP, int MODE, bool HALF, int CAP = 24>
+__global__ void __launch_bounds__(Cfg<HD, MT, WN, NP, CAP>::THREADS, 1)
 attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap) {
-  using C = Cfg<HD, MT, WN, NP>;
+  using C = Cfg<HD, MT, WN, NP, CAP>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t ring = base;
