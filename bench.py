@@ -181,6 +181,53 @@ def bench_gdn(dev, steps, warmup, hbm_gbs):
     }
 
 
+def bench_attn_extra(dev, hbm_gbs, steps=5):
+    """Speculative verify (C3) and chunked-prefill extend (C4, full and sliding-window) through the plugin
+    front-end: us/call, HBM GB/s for the HBM-bound verify, TFLOP/s for the tensor-bound extend."""
+    from greenattention_b200 import attn_decode
+
+    out = {}
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(kw, select):
+        run = select(kw)
+        if not callable(run):
+            return {"declined": run}
+        o = torch.empty(kw["q"].shape, dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            run(**dict(kw, out=o))
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for s, e in ev:
+            flush.zero_()
+            s.record()
+            run(**dict(kw, out=o))
+            e.record()
+        torch.cuda.synchronize()
+        ms = sorted(s.elapsed_time(e) for s, e in ev)
+        return ms[len(ms) // 2]
+
+    kw = W.c3_spec_verify(dev)
+    ms = timed(kw, attn_decode.select)
+    if isinstance(ms, dict):
+        out["verify"] = ms
+    else:
+        nb, fl = W.attn_kv_bytes(kw), W.attn_flops(kw)
+        out["verify"] = {"workload": "C3 verify: B=64, q_len 5, QH32/KVH8, hd128, prefix 8k", "us_per_call": ms * 1e3,
+                         "hbm_gbs": nb / ms / 1e6, "hbm_frac": nb / ms / 1e6 / hbm_gbs, "tflops": fl / ms / 1e9}
+    del kw
+    for name, window in (("extend_full", None), ("extend_window1024", 1024)):
+        kw = W.c4_extend(dev, window=window)
+        ms = timed(kw, attn_decode.select_extend)
+        if isinstance(ms, dict):
+            out[name] = ms
+        else:
+            fl = W.attn_flops(kw)
+            out[name] = {"workload": f"C4 extend: B=8, 2048 new on 16k prefix, QH16/KVH8, hd256, window={window}",
+                         "us_per_call": ms * 1e3, "tflops": fl / ms / 1e9, "flops": fl}
+        del kw
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -190,6 +237,7 @@ def main():
     ap.add_argument("--batch", type=int, default=128, help="requests per GPU (the named configuration uses 128)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gdn", action="store_true")
+    ap.add_argument("--extra", action="store_true", help="also time the verify (C3) and extend (C4) configurations")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "green" else args.warmup
 
@@ -306,6 +354,13 @@ def main():
                 line["gdn"] = bench_gdn(dev, max(args.steps, 10), 3, hbm_gbs)
             except Exception as exc:  # noqa: BLE001 - the decode line must still print
                 line["gdn"] = {"error": repr(exc)}
+        if args.extra:
+            try:
+                del kw, call
+                torch.cuda.empty_cache()
+                line["attn_extra"] = bench_attn_extra(dev, hbm_gbs)
+            except Exception as exc:  # noqa: BLE001
+                line["attn_extra"] = {"error": repr(exc)}
         if world == 1 and not args.no_cpu_baseline:
             val, cores, sample, _ = cpu_oracle_sample(32, seed=7)
             line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}

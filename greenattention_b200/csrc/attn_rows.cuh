@@ -66,7 +66,6 @@ struct AttnDev {
   int box_tok;       // tokens per TMA box = min(page_size, TN)
   int max_q;         // decode/verify: query tokens per request are capped here (rows <= 16*MT)
   int bq;            // extend: query tokens per row block
-  int dbg;
   // split-KV workspace
   int* status;
   int* prefix;       // [batch + 1] exclusive prefix of per-request tile counts (written by CTA 0)
@@ -208,7 +207,7 @@ struct SliceWalker {
 
 constexpr int gcd_(int a, int b) { return b == 0 ? a : gcd_(b, a % b); }
 
-template <int HD, int MT, int WN, int NP_ = 4, int CAP_ = 24>
+template <int HD, int MT, int WN, int NP_ = 4, int CAP_ = 24, int SUB_ = 1>
 struct Cfg {
   static constexpr int ATOMS = HD / 128;
   static constexpr int NCW = MT * WN;               // consumer warps
@@ -217,7 +216,9 @@ struct Cfg {
   static constexpr int NP = NP_;
   static constexpr int THREADS = (NCW + NP) * 32;
   static constexpr int ROWS = MT * 16;
-  static constexpr int STAGE_BYTES = 2 * ATOMS * ATOM_BYTES;  // K slabs then V slabs
+  static constexpr int SUB = SUB_;                               // 64-token tiles per ring stage
+  static constexpr int TILE_BYTES = 2 * ATOMS * ATOM_BYTES;      // one tile: K slabs then V slabs
+  static constexpr int STAGE_BYTES = SUB * TILE_BYTES;
   static constexpr int V_OFF = ATOMS * ATOM_BYTES;
   static constexpr int PITCH = HD + 4;              // floats per row of the merge buffer
   static constexpr int MERGE_BYTES = WN > 1 ? ROWS * PITCH * 4 + ROWS * 8 : 0;
@@ -261,54 +262,57 @@ __device__ __forceinline__ int pt_lookup(const AttnDev& p, PtWindow& w, int b, i
   return __shfl_sync(0xffffffffu, w.cur, e - w.base);
 }
 
+// Fills one ring stage with the `nsub` consecutive 64-token tiles that start at tile `tt` of segment `s`.
 template <class C>
-__device__ __forceinline__ bool produce_tile(const AttnDev& p, const CUtensorMap* kmap, const CUtensorMap* vmap,
-                                             const Seg& s, int tt, uint32_t stage_addr, uint32_t full_bar, int lane,
-                                             PtWindow& win) {
-  const int n0 = tt * TN;
-  bool ok = true;
+__device__ __forceinline__ void produce_stage(const AttnDev& p, const CUtensorMap* kmap, const CUtensorMap* vmap,
+                                              const Seg& s, int tt, int nsub, uint32_t stage_addr, uint32_t full_bar,
+                                              int lane, PtWindow& win) {
   if (p.use_tma) {
     const int nbox = TN / p.box_tok;
-    int valid = 0;  // boxes that hold at least one live token
-    for (int i = 0; i < nbox; ++i) valid += (n0 + i * p.box_tok) < s.L;
-    if (lane == 0) mbar_expect_tx(full_bar, static_cast<uint32_t>(valid) * p.box_tok * 128 * C::ATOMS * 2);
+    int boxes = 0;  // boxes that hold at least one live token
+    for (int u = 0; u < nsub; ++u)
+      for (int i = 0; i < nbox; ++i) boxes += ((tt + u) * TN + i * p.box_tok) < s.L;
+    if (lane == 0) mbar_expect_tx(full_bar, static_cast<uint32_t>(boxes) * p.box_tok * 128 * C::ATOMS * 2);
     __syncwarp();
-    for (int i = 0; i < valid; ++i) {
-      const int n = n0 + i * p.box_tok;
-      int page = pt_lookup(p, win, s.b, n >> p.page_shift, lane);
-      if (page < 0 || page >= p.num_pages) {
-        if (lane == 0) atomicExch(p.status, GA_ST_BAD_PAGE);  // recorded; an out-of-range box reads as zeros
-        ok = false;
-      }
-      if (lane < C::ATOMS * 2) {
-        const int is_v = lane / C::ATOMS, atom = lane - is_v * C::ATOMS;
-        uint32_t dst = stage_addr + (is_v ? C::V_OFF : 0) + atom * ATOM_BYTES + i * p.box_tok * 128;
-        tma_load_4d(dst, is_v ? vmap : kmap, full_bar, atom * 128, s.h, n & p.page_mask, page);
+    for (int u = 0; u < nsub; ++u) {
+      const int n0 = (tt + u) * TN;
+      for (int i = 0; i < nbox; ++i) {
+        const int n = n0 + i * p.box_tok;
+        if (n >= s.L) break;
+        int page = pt_lookup(p, win, s.b, n >> p.page_shift, lane);
+        if (page < 0 || page >= p.num_pages) {
+          if (lane == 0) atomicExch(p.status, GA_ST_BAD_PAGE);  // recorded; an out-of-range box reads as zeros
+        }
+        if (lane < C::ATOMS * 2) {
+          const int is_v = lane / C::ATOMS, atom = lane - is_v * C::ATOMS;
+          uint32_t dst = stage_addr + u * C::TILE_BYTES + (is_v ? C::V_OFF : 0) + atom * ATOM_BYTES + i * p.box_tok * 128;
+          tma_load_4d(dst, is_v ? vmap : kmap, full_bar, atom * 128, s.h, n & p.page_mask, page);
+        }
       }
     }
   } else {
-    for (int r = lane; r < TN; r += 32) {
-      int n = n0 + r;
-      if (n < s.L) {
-        int page = p.pt[s.b * p.pt_s0 + (n >> p.page_shift) * p.pt_s1];
-        if (page < 0 || page >= p.num_pages) {
-          atomicExch(p.status, GA_ST_BAD_PAGE);
-          page = 0;
-          ok = false;
-        }
-        const uint8_t* ksrc = p.k + page * p.k_s0 + (n & p.page_mask) * p.k_s1 + s.h * p.k_s2;
-        const uint8_t* vsrc = p.v + page * p.v_s0 + (n & p.page_mask) * p.v_s1 + s.h * p.v_s2;
+    for (int u = 0; u < nsub; ++u) {
+      for (int r = lane; r < TN; r += 32) {
+        int n = (tt + u) * TN + r;
+        if (n < s.L) {
+          int page = p.pt[s.b * p.pt_s0 + (n >> p.page_shift) * p.pt_s1];
+          if (page < 0 || page >= p.num_pages) {
+            atomicExch(p.status, GA_ST_BAD_PAGE);
+            page = 0;
+          }
+          const uint8_t* ksrc = p.k + page * p.k_s0 + (n & p.page_mask) * p.k_s1 + s.h * p.k_s2;
+          const uint8_t* vsrc = p.v + page * p.v_s0 + (n & p.page_mask) * p.v_s1 + s.h * p.v_s2;
 #pragma unroll
-        for (int c = 0; c < C::ATOMS * 8; ++c) {
-          uint32_t off = (c >> 3) * ATOM_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-          cp_async_16(stage_addr + off, ksrc + c * 16);
-          cp_async_16(stage_addr + C::V_OFF + off, vsrc + c * 16);
+          for (int c = 0; c < C::ATOMS * 8; ++c) {
+            uint32_t off = u * C::TILE_BYTES + (c >> 3) * ATOM_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+            cp_async_16(stage_addr + off, ksrc + c * 16);
+            cp_async_16(stage_addr + C::V_OFF + off, vsrc + c * 16);
+          }
         }
       }
     }
     cp_async_mbar_arrive_noinc(full_bar);
   }
-  return ok;
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -372,17 +376,30 @@ __device__ __forceinline__ void consume_tile(const AttnDev& p, const Seg& s, int
   float sc[8][4];
 #pragma unroll
   for (int j = 0; j < 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+  // B fragments of four 8-token groups are fetched first, then the MMAs run k-step-major so that
+  // consecutive MMAs accumulate into different registers (no back-to-back dependency).
+  const uint32_t xr = static_cast<uint32_t>(lrow) << 4;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int row = j * 8 + lrow;
+  for (int half = 0; half < 2; ++half) {
+    uint32_t kb[4][C::ATOMS * 2][4];
 #pragma unroll
-    for (int q4 = 0; q4 < C::ATOMS * 2; ++q4) {  // 64 dims (two k-steps) per ldmatrix.x4
-      int c = q4 * 4 + lmat;                     // 16-byte chunk of the head vector
-      uint32_t addr = stage_addr + (c >> 3) * ATOM_BYTES + row * 128 + (((c & 7) ^ lrow) << 4);
-      uint32_t r0, r1, r2, r3;
-      ldsm_x4(addr, r0, r1, r2, r3);
-      mma_e4m3_16x8x32(sc[j], qf[q4 * 2], r0, r1);
-      mma_e4m3_16x8x32(sc[j], qf[q4 * 2 + 1], r2, r3);
+    for (int jj = 0; jj < 4; ++jj) {
+      const uint32_t rowaddr = stage_addr + ((half * 4 + jj) * 8 + lrow) * 128;
+#pragma unroll
+      for (int q4 = 0; q4 < C::ATOMS * 2; ++q4) {  // 64 dims (two k-steps) per ldmatrix.x4
+        const int c = q4 * 4 + lmat;               // 16-byte chunk of the head vector
+        ldsm_x4(rowaddr + (c >> 3) * ATOM_BYTES + ((static_cast<uint32_t>(c & 7) << 4) ^ xr), kb[jj][q4][0],
+                kb[jj][q4][1], kb[jj][q4][2], kb[jj][q4][3]);
+      }
+    }
+#pragma unroll
+    for (int q4 = 0; q4 < C::ATOMS * 2; ++q4) {
+#pragma unroll
+      for (int sub = 0; sub < 2; ++sub) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          mma_e4m3_16x8x32(sc[half * 4 + jj], qf[q4 * 2 + sub], kb[jj][q4][sub * 2], kb[jj][q4][sub * 2 + 1]);
+      }
     }
   }
 
@@ -494,18 +511,30 @@ __device__ __forceinline__ void consume_tile(const AttnDev& p, const Seg& s, int
   const uint32_t vbase = stage_addr + C::V_OFF;
 #pragma unroll
   for (int c2 = 0; c2 < 2; ++c2) {
-    const int row = (c2 * 4 + lmat) * 8 + lrow;
+    const uint32_t rowaddr = vbase + ((c2 * 4 + lmat) * 8 + lrow) * 128;
 #pragma unroll
-    for (int db = 0; db < C::ATOMS * 8; ++db) {
-      uint32_t addr = vbase + (db >> 3) * ATOM_BYTES + row * 128 + (((db & 7) ^ lrow) << 4);
-      uint32_t r0, r1, r2, r3;
-      ldsm_x4_trans(addr, r0, r1, r2, r3);
-      const uint32_t e0 = prmt(r0, r1, 0x6420), e1 = prmt(r2, r3, 0x6420);
-      const uint32_t o0 = prmt(r0, r1, 0x7531), o1 = prmt(r2, r3, 0x7531);
-      mma_e4m3_16x8x32(acc.o[db * 2], pa[c2], e0, e1);
-      mma_e4m3_16x8x32(acc.o[db * 2], pl[c2], e0, e1);
-      mma_e4m3_16x8x32(acc.o[db * 2 + 1], pa[c2], o0, o1);
-      mma_e4m3_16x8x32(acc.o[db * 2 + 1], pl[c2], o0, o1);
+    for (int grp = 0; grp < C::ATOMS * 2; ++grp) {  // four 16-dim blocks at a time
+      uint32_t ve[4][2], vo[4][2];
+#pragma unroll
+      for (int d4 = 0; d4 < 4; ++d4) {
+        const int db = grp * 4 + d4;
+        uint32_t r0, r1, r2, r3;
+        ldsm_x4_trans(rowaddr + (db >> 3) * ATOM_BYTES + ((static_cast<uint32_t>(db & 7) << 4) ^ xr), r0, r1, r2, r3);
+        ve[d4][0] = prmt(r0, r1, 0x6420);
+        ve[d4][1] = prmt(r2, r3, 0x6420);
+        vo[d4][0] = prmt(r0, r1, 0x7531);
+        vo[d4][1] = prmt(r2, r3, 0x7531);
+      }
+#pragma unroll
+      for (int d4 = 0; d4 < 4; ++d4) {
+        mma_e4m3_16x8x32(acc.o[(grp * 4 + d4) * 2], pa[c2], ve[d4][0], ve[d4][1]);
+        mma_e4m3_16x8x32(acc.o[(grp * 4 + d4) * 2 + 1], pa[c2], vo[d4][0], vo[d4][1]);
+      }
+#pragma unroll
+      for (int d4 = 0; d4 < 4; ++d4) {
+        mma_e4m3_16x8x32(acc.o[(grp * 4 + d4) * 2], pl[c2], ve[d4][0], ve[d4][1]);
+        mma_e4m3_16x8x32(acc.o[(grp * 4 + d4) * 2 + 1], pl[c2], vo[d4][0], vo[d4][1]);
+      }
     }
   }
 }
@@ -740,11 +769,11 @@ __device__ __forceinline__ void store_pair(const AttnDev& p, const Seg& s, int h
 // MODE 0: persistent split-KV over the tile stream (decode / verify). MODE 1: one row block of
 // p.bq query tokens per CTA over everything it can see (extend). HALF: at most 8 live rows per CTA
 // (decode with GQA <= 8): rows 8..15 of the MMA tile carry no accumulators.
-template <int HD, int MT, int WN, int NP, int MODE, bool HALF, int CAP = 24>
-__global__ void __launch_bounds__(Cfg<HD, MT, WN, NP, CAP>::THREADS, 1)
+template <int HD, int MT, int WN, int NP, int MODE, bool HALF, int CAP = 24, int SUB = 1, int OCC = 1>
+__global__ void __launch_bounds__(Cfg<HD, MT, WN, NP, CAP, SUB>::THREADS, OCC)
 attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap) {
-  using C = Cfg<HD, MT, WN, NP, CAP>;
+  using C = Cfg<HD, MT, WN, NP, CAP, SUB>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t ring = base;
@@ -849,14 +878,15 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
         s = one;
         one_pending = false;
       }
-      for (int tt = s.t_lo; tt < s.t_hi; ++tt, ++it) {
+      for (int tt = s.t_lo; tt < s.t_hi; tt += C::SUB, ++it) {
         if ((it % C::NP) != pw) continue;
         const int stage = it % C::NST, use = it / C::NST;
         if (use > 0 && !mbar_wait(bars + (C::NST + stage) * 8, (use - 1) & 1)) {
           if (lane == 0) atomicExch(p.status, GA_ST_WAIT_EMPTY);
           return;
         }
-        produce_tile<C>(p, &kmap, &vmap, s, tt, ring + stage * C::STAGE_BYTES, bars + stage * 8, lane, win);
+        const int nsub = s.t_hi - tt < C::SUB ? s.t_hi - tt : C::SUB;
+        produce_stage<C>(p, &kmap, &vmap, s, tt, nsub, ring + stage * C::STAGE_BYTES, bars + stage * 8, lane, win);
       }
     }
     return;
@@ -883,7 +913,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
       const float kds = p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f;
       const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
       const float sl2 = p.scale_log2 * kds;
-      for (int tt = s.t_lo; tt < s.t_hi; ++tt, ++it) {
+      for (int tt = s.t_lo; tt < s.t_hi; tt += C::SUB, ++it) {
         if (WN > 1 && (it % WN) != wn) continue;
         const int stage = it % C::NST, use = it / C::NST;
         if (!failed && !mbar_wait(bars + stage * 8, use & 1)) {
@@ -891,7 +921,9 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
           failed = true;
         }
         if (failed) continue;
-        consume_tile8<C>(p, s, tt, ring + stage * C::STAGE_BYTES, qf, pos, sl2, acc, lane);
+#pragma unroll 1
+        for (int u = 0; u < C::SUB && tt + u < s.t_hi; ++u)
+          consume_tile8<C>(p, s, tt + u, ring + stage * C::STAGE_BYTES + u * C::TILE_BYTES, qf, pos, sl2, acc, lane);
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + (C::NST + stage) * 8);
@@ -984,7 +1016,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
     const float kds = p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f;
     const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
     const float sl2 = p.scale_log2 * kds;
-    for (int tt = s.t_lo; tt < s.t_hi; ++tt, ++it) {
+    for (int tt = s.t_lo; tt < s.t_hi; tt += C::SUB, ++it) {
       if (WN > 1 && (it % WN) != wn) continue;
       const int stage = it % C::NST, use = it / C::NST;
       // A wait that runs out is recorded once; the warp then drains its loops without touching the
@@ -994,7 +1026,12 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
         failed = true;
       }
       if (failed) continue;
-      if (any_rows) consume_tile<C, HALF>(p, s, tt, ring + stage * C::STAGE_BYTES, qf, pos, hi_rows, sl2, acc, lane);
+      if (any_rows) {
+#pragma unroll 1
+        for (int u = 0; u < C::SUB && tt + u < s.t_hi; ++u)
+          consume_tile<C, HALF>(p, s, tt + u, ring + stage * C::STAGE_BYTES + u * C::TILE_BYTES, qf, pos, hi_rows, sl2,
+                                acc, lane);
+      }
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + (C::NST + stage) * 8);
