@@ -14,6 +14,7 @@
 
 #include "../../include/green_attention.h"
 #include "attn_rows.cuh"
+#include "attn_tc.cuh"
 #include "gdn_recurrent.cuh"
 
 namespace {
@@ -119,6 +120,17 @@ const AttnInstance* decode_instance(int hd, int rows) {
 const AttnInstance* extend_instance(int hd) {
   static const AttnInstance e128 = make_instance<128, 8, 1, 4, 1>();
   static const AttnInstance e256 = make_instance<256, 8, 1, 2, 1>();
+  return hd == 128 ? &e128 : &e256;
+}
+
+template <int HD>
+AttnInstance make_tc_instance() {
+  return {ga::attn::tc::attn_tc_kernel<HD>, ga::attn::tc::THREADS, ga::attn::tc::TcCfg<HD>::SMEM_BYTES, 128, 1};
+}
+// tcgen05 extend kernel (128 query rows per CTA).
+const AttnInstance* extend_tc_instance(int hd) {
+  static const AttnInstance e128 = make_tc_instance<128>();
+  static const AttnInstance e256 = make_tc_instance<256>();
   return hd == 128 ? &e128 : &e256;
 }
 
@@ -269,7 +281,7 @@ int ga_init(int device) {
   for (int hd : {128, 256}) {
     for (int rows : {8, 16, 32, 64, 128})
       if (set_smem(*decode_instance(hd, rows))) return 1;
-    if (set_smem(*extend_instance(hd))) return 1;
+    if (set_smem(*extend_instance(hd)) || set_smem(*extend_tc_instance(hd))) return 1;
   }
   GA_CUDA(cudaSetDevice(prev));
   std::lock_guard<std::mutex> lock(g_mu);
@@ -328,7 +340,7 @@ constexpr int kNoAllocMaxBatch = 1024;   // requests per call
 constexpr int kNoAllocMaxSm = 160;       // CTAs of the persistent grid (one per SM)
 constexpr int kNoAllocRows = 16;         // max_seqlen_q * (q_heads / kv_heads) per (request, kv head)
 constexpr size_t kNoAllocPrefixBytes = ((kNoAllocMaxBatch + 1) * 4 + 255) / 256 * 256;
-constexpr size_t kNoAllocLseBytes = static_cast<size_t>(2 * kNoAllocMaxSm) * kNoAllocRows * 4;
+constexpr size_t kNoAllocLseBytes = static_cast<size_t>(2 * 2 * kNoAllocMaxSm) * kNoAllocRows * 4;  // up to 2 CTAs per SM
 constexpr size_t kNoAllocOBytes = static_cast<size_t>(2 * kNoAllocMaxSm) * kNoAllocRows * 256 * 4;
 constexpr size_t kNoAllocBytes = kWsHeader + kNoAllocPrefixBytes + kNoAllocLseBytes + kNoAllocOBytes;  // ~5.03 MiB
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
@@ -350,8 +362,12 @@ int ga_attn_decode_noalloc(const GaAttnParams* a, void* stream) {
   if (a->batch > kNoAllocMaxBatch)
     return fail("ga_attn_decode_noalloc: batch %d exceeds the built-in scratch (%d requests); use ga_attn_decode "
                 "with a workspace", a->batch, kNoAllocMaxBatch);
-  if (sm > kNoAllocMaxSm)
-    return fail("ga_attn_decode_noalloc: %d SMs exceed the built-in scratch (%d CTAs)", sm, kNoAllocMaxSm);
+  const AttnInstance* k = decode_instance(a->head_dim, rows);  // rows <= 16: a 16-row instance
+  const int grid = sm * k->occ;  // same grid as ga_attn_decode, so both entry points cut the work identically
+  if (sm > kNoAllocMaxSm || static_cast<size_t>(2 * grid) * kNoAllocRows * a->head_dim * 4 > kNoAllocOBytes ||
+      static_cast<size_t>(2 * grid) * kNoAllocRows * 4 > kNoAllocLseBytes)
+    return fail("ga_attn_decode_noalloc: a grid of %d CTAs on %d SMs exceeds the built-in scratch (%d SMs)", grid, sm,
+                kNoAllocMaxSm);
   if (g_noalloc_ptr[dev] == nullptr) {
     // First call on this device (it is the current one): resolve the device address of the array.
     void* ptr = nullptr;
@@ -370,12 +386,11 @@ int ga_attn_decode_noalloc(const GaAttnParams* a, void* stream) {
   d.ws_o = reinterpret_cast<float*>(ws + kWsHeader + kNoAllocPrefixBytes + kNoAllocLseBytes);
   d.max_q = a->max_seqlen_q;
   d.bq = 0;
-  const AttnInstance* k = decode_instance(a->head_dim, rows);  // rows <= 16: the 16-row instance
-  k->fn<<<sm, k->threads, k->smem, st>>>(d, kmap, vmap);
+  k->fn<<<grid, k->threads, k->smem, st>>>(d, kmap, vmap);
   GA_CUDA(cudaGetLastError());
   dim3 cgrid(a->batch, a->kv_heads);
-  if (a->head_dim == 128) ga::attn::attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(d, sm, k->rows);
-  else ga::attn::attn_combine_kernel<256><<<cgrid, 128, 0, st>>>(d, sm, k->rows);
+  if (a->head_dim == 128) ga::attn::attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(d, grid, k->rows);
+  else ga::attn::attn_combine_kernel<256><<<cgrid, 128, 0, st>>>(d, grid, k->rows);
   GA_CUDA(cudaGetLastError());
   g_launches = 2;
   return 0;
@@ -399,7 +414,13 @@ int ga_attn_extend(const GaAttnParams* a, void* stream) {
     g_launches = 0;
     return 0;
   }
-  const AttnInstance* k = extend_instance(a->head_dim);
+  // The tcgen05 kernel wants TMA-sized pages and 16-byte aligned q / out rows; anything else runs on the
+  // warp-level MMA kernel.
+  const uintptr_t qa = reinterpret_cast<uintptr_t>(a->q), oa = reinterpret_cast<uintptr_t>(a->out);
+  const int qel = a->q_is_bf16 ? 8 : 16;
+  const bool tc_ok = d.use_tma && qa % 16 == 0 && oa % 16 == 0 && a->q_stride_tok % qel == 0 &&
+                     a->q_stride_head % qel == 0 && a->o_stride_tok % 8 == 0 && a->o_stride_head % 8 == 0;
+  const AttnInstance* k = tc_ok ? extend_tc_instance(a->head_dim) : extend_instance(a->head_dim);
   dim3 grid(static_cast<unsigned>(blocks), a->kv_heads);
   k->fn<<<grid, k->threads, k->smem, static_cast<cudaStream_t>(stream)>>>(d, kmap, vmap);
   GA_CUDA(cudaGetLastError());

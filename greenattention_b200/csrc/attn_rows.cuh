@@ -205,6 +205,52 @@ struct SliceWalker {
   }
 };
 
+// Extend: row block `x` of the call (heaviest, i.e. latest, blocks first) for kv head `h`. Every warp runs an
+// identical copy. `tile` is the KV tile size the caller iterates in. Returns false when x is past the last block.
+__device__ __forceinline__ bool extend_block(const AttnDev& p, int x_in, int h, int tile, int lane, Seg& one) {
+  int total = 0, found_b = -1, found_pre = 0, pre = 0;
+  for (int b0 = 0; b0 < p.batch; b0 += 32) {
+    int bb = b0 + lane;
+    int ql = bb < p.batch ? p.cu[bb + 1] - p.cu[bb] : 0;
+    total += (ql + p.bq - 1) / p.bq;
+  }
+#pragma unroll
+  for (int d = 16; d; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+  const int x = total - 1 - x_in;
+  if (x < 0) return false;
+  for (int b0 = 0; b0 < p.batch && found_b < 0; b0 += 32) {
+    int bb = b0 + lane;
+    int ql = bb < p.batch ? p.cu[bb + 1] - p.cu[bb] : 0;
+    int nb = (ql + p.bq - 1) / p.bq;
+    int incl = warp_incl_scan(nb, lane);
+    unsigned hit = __ballot_sync(0xffffffffu, pre + incl > x);
+    if (hit) {
+      int src = __ffs(hit) - 1;
+      found_b = b0 + src;
+      found_pre = pre + __shfl_sync(0xffffffffu, incl, src) - __shfl_sync(0xffffffffu, nb, src);
+    } else {
+      pre += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  if (found_b < 0) return false;
+  const int b = found_b, j = x - found_pre;
+  const int ql = p.cu[b + 1] - p.cu[b];
+  one.b = b;
+  one.h = h;
+  one.q0 = p.cu[b] + j * p.bq;
+  one.nq = min(p.bq, ql - j * p.bq);
+  one.L = p.seqlens[b];
+  one.pos0 = one.L - ql + j * p.bq;
+  int last = one.pos0 + one.nq - 1;
+  if (last > one.L - 1) last = one.L - 1;
+  one.t_hi = last >= 0 ? last / tile + 1 : 0;
+  int lower = p.window_left >= 0 ? one.pos0 - p.window_left : 0;
+  one.t_lo = lower > 0 ? lower / tile : 0;
+  if (one.t_lo > one.t_hi) one.t_lo = one.t_hi;
+  one.slot = -1;
+  return true;
+}
+
 constexpr int gcd_(int a, int b) { return b == 0 ? a : gcd_(b, a % b); }
 
 template <int HD, int MT, int WN, int NP_ = 4, int CAP_ = 24, int SUB_ = 1>
@@ -812,50 +858,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
       if (lane == 0) p.prefix[p.batch] = pre;
     }
   } else {
-    // Row block x of the call, heaviest (latest) blocks first.
-    int total = 0, found_b = -1, found_pre = 0, pre = 0;
-    for (int b0 = 0; b0 < p.batch; b0 += 32) {
-      int bb = b0 + lane;
-      int ql = bb < p.batch ? p.cu[bb + 1] - p.cu[bb] : 0;
-      total += (ql + p.bq - 1) / p.bq;
-    }
-#pragma unroll
-    for (int d = 16; d; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
-    int x = total - 1 - static_cast<int>(blockIdx.x);
-    if (x >= 0) {
-      for (int b0 = 0; b0 < p.batch && found_b < 0; b0 += 32) {
-        int bb = b0 + lane;
-        int ql = bb < p.batch ? p.cu[bb + 1] - p.cu[bb] : 0;
-        int nb = (ql + p.bq - 1) / p.bq;
-        int incl = warp_incl_scan(nb, lane);
-        unsigned hit = __ballot_sync(0xffffffffu, pre + incl > x);
-        if (hit) {
-          int src = __ffs(hit) - 1;
-          found_b = b0 + src;
-          found_pre = pre + __shfl_sync(0xffffffffu, incl, src) - __shfl_sync(0xffffffffu, nb, src);
-        } else {
-          pre += __shfl_sync(0xffffffffu, incl, 31);
-        }
-      }
-    }
-    if (found_b >= 0) {
-      int b = found_b, j = x - found_pre;
-      int ql = p.cu[b + 1] - p.cu[b];
-      one.b = b;
-      one.h = blockIdx.y;
-      one.q0 = p.cu[b] + j * p.bq;
-      one.nq = min(p.bq, ql - j * p.bq);
-      one.L = p.seqlens[b];
-      one.pos0 = one.L - ql + j * p.bq;
-      int last = one.pos0 + one.nq - 1;
-      if (last > one.L - 1) last = one.L - 1;
-      one.t_hi = last >= 0 ? last / TN + 1 : 0;
-      int lower = p.window_left >= 0 ? one.pos0 - p.window_left : 0;
-      one.t_lo = lower > 0 ? lower / TN : 0;
-      if (one.t_lo > one.t_hi) one.t_lo = one.t_hi;
-      one.slot = -1;
-      one_pending = true;
-    }
+    one_pending = extend_block(p, static_cast<int>(blockIdx.x), static_cast<int>(blockIdx.y), TN, lane, one);
   }
 
   Seg s;

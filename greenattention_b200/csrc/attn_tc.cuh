@@ -1,0 +1,438 @@
+// FP8 paged attention for large query blocks (extend / chunked prefill) on the 5th-generation tensor
+// cores: tcgen05.mma (kind::f8f6f4, e4m3 x e4m3 -> f32) with accumulators in tensor memory.
+//
+// Replaces the reference's SM90 WGMMA extend kernel (csrc/sm90/attn_decode_fp8/extend_kernel.cuh:162-457;
+// work decomposition extend_kernel.cuh:140-160) for head_dim 128 and 256, any GQA, causal with an optional
+// left window. Same math as the reference kernels: bf16 Q rounded to e4m3, S = scale * k_descale * Q K^T,
+// bottom-right causal mask and left window, online softmax in the log2 domain, P rounded to e4m3, O = v_descale
+// * P V / l, natural-log LSE (kernel.cuh:468-474,489-496,621-653).
+//
+// One CTA = 128 query rows (128 / GQA tokens x the GQA heads of one kv head) against the keys they can see,
+// 128 keys per iteration:
+//   * warp 4 (producer) gathers K and V pages with TMA (128-byte swizzle, one box per page and 128-byte head
+//     slice, never multicast) into two 2-stage rings;
+//   * warp 5 (one lane) issues the MMAs: S = Q K^T with both operands K-major straight from the swizzled
+//     tiles, and O += P V with P as a K-major A operand from shared memory and V as an MN-major B operand, i.e.
+//     the [token, dim] page layout as it is: no transpose of V anywhere. S (2 x 128 columns, double
+//     buffered) and O (head_dim columns) live in tensor memory;
+//   * warps 0-3 (softmax): thread = query row = tensor-memory lane. Each thread reads its S row with
+//     tcgen05.ld, does mask / max / exp2 without any cross-thread traffic, writes P as two e4m3 terms
+//     (4 significant bits + residual, so a probability carries ~2^-8 relative error) into swizzled shared
+//     memory, and rescales O in tensor memory only when its running max moved by more than 1.5 in log2 (the
+//     stale max keeps P below the e4m3 limit: 2^(7 + 1.5) < 448).
+// Every wait is bounded; a wait that runs out records a status word and the CTA drains to its common exit,
+// where tensor memory is released.
+#pragma once
+
+#include "attn_rows.cuh"
+
+namespace ga {
+namespace attn {
+namespace tc {
+
+constexpr int TM = 128;             // query rows per CTA
+constexpr int TNK = 128;            // keys per iteration
+constexpr int SLAB = TNK * 128;     // one 128-byte-wide swizzled slab of a 128-row tile
+constexpr float TC_SHIFT = 7.f;     // P = 2^(s - m + 7)
+constexpr float TC_LAZY = 1.5f;     // rescale O only when the row max grew by more than this (log2 units)
+constexpr int THREADS = 192;
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= static_cast<uint64_t>(1) << 46;  // descriptor version of sm_100
+  d |= static_cast<uint64_t>(2) << 61;  // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor of kind::f8f6f4: f32 accumulate, e4m3 A and B, A K-major, B K-major or MN-major.
+__device__ __forceinline__ uint32_t instr_desc(int m, int n, int b_mn_major) {
+  return (1u << 4) | (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, int accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <int HD>
+struct TcCfg {
+  static constexpr int ATOMS = HD / 128;
+  static constexpr int Q_BYTES = ATOMS * SLAB;
+  static constexpr int P_BYTES = SLAB;                // one e4m3 term of P: 128 rows x 128 keys
+  static constexpr int KV_BYTES = ATOMS * SLAB;       // one K (or V) tile
+  static constexpr int NKV = HD == 128 ? 3 : 2;       // ring depth of each of the K and V rings
+  static constexpr int Q_OFF = 0;
+  static constexpr int P_OFF = Q_OFF + Q_BYTES;       // [buffer 0|1][hi|lo]
+  static constexpr int K_OFF = P_OFF + 4 * P_BYTES;
+  static constexpr int V_OFF = K_OFF + NKV * KV_BYTES;
+  static constexpr int BAR_OFF = V_OFF + NKV * KV_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + BAR_OFF + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int S_COL = 0;                     // S buffers at columns 0 and 128
+  static constexpr int O_COL = 256;
+  static_assert(SMEM_BYTES <= SMEM_OPTIN, "shared memory");
+};
+
+// Bounded wait that never returns early from the kernel: a wait that runs out is recorded and every later
+// wait of this thread is skipped, so all warps still reach the common exit.
+__device__ __forceinline__ void wait_or_flag(uint32_t bar, uint32_t parity, bool& failed, int* status, int code) {
+  if (failed) return;
+  if (!mbar_wait(bar, parity)) {
+    failed = true;
+    atomicExch(status, code);
+  }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
+               const __grid_constant__ CUtensorMap vmap) {
+  using C = TcCfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t sQ = base + C::Q_OFF, sP = base + C::P_OFF, sK = base + C::K_OFF, sV = base + C::V_OFF;
+  const uint32_t bars = base + C::BAR_OFF;
+  // barrier slots
+  const uint32_t b_q = bars, b_sfull = bars + 8, b_sfree = bars + 24, b_pready = bars + 40, b_pfree = bars + 56;
+  const uint32_t b_kfull = bars + 72, b_kempty = b_kfull + 8 * C::NKV, b_vfull = b_kempty + 8 * C::NKV,
+                 b_vempty = b_vfull + 8 * C::NKV;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 72 + 32 * C::NKV);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    mbar_init(b_q, 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(b_sfull + 8 * i, 1);
+      mbar_init(b_sfree + 8 * i, 128);
+      mbar_init(b_pready + 8 * i, 128);
+      mbar_init(b_pfree + 8 * i, 1);
+    }
+    for (int i = 0; i < C::NKV; ++i) {
+      mbar_init(b_kfull + 8 * i, 1);
+      mbar_init(b_kempty + 8 * i, 1);
+      mbar_init(b_vfull + 8 * i, 1);
+      mbar_init(b_vempty + 8 * i, 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(C::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  Seg s;
+  const bool have = extend_block(p, static_cast<int>(blockIdx.x), static_cast<int>(blockIdx.y), TNK, lane, s);
+  const int n_tiles = have ? s.t_hi - s.t_lo : 0;
+  bool failed = false;
+
+  if (have && warp == 4) {
+    // ---------------------------------------------------------------- producer: K and V tiles by TMA
+    PtWindow win;
+    win.b = -1;
+    win.base = win.cur = win.nxt = 0;
+    if (lane == 0) {
+      tma_prefetch_desc(&kmap);
+      tma_prefetch_desc(&vmap);
+    }
+    const int nbox = TNK / p.box_tok;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int st = t % C::NKV, use = t / C::NKV;
+      const int n0 = (s.t_lo + t) * TNK;
+      int boxes = 0;
+      for (int i = 0; i < nbox; ++i) boxes += (n0 + i * p.box_tok) < s.L;
+      const uint32_t bytes = static_cast<uint32_t>(boxes) * p.box_tok * 128 * C::ATOMS;
+#pragma unroll 1
+      for (int kv = 0; kv < 2; ++kv) {
+        const uint32_t full = (kv ? b_vfull : b_kfull) + 8 * st, empty = (kv ? b_vempty : b_kempty) + 8 * st;
+        if (use > 0) wait_or_flag(empty, (use - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        if (failed) break;
+        if (lane == 0) mbar_expect_tx(full, bytes);
+        __syncwarp();
+        for (int i = 0; i < boxes; ++i) {
+          const int n = n0 + i * p.box_tok;
+          int page = pt_lookup(p, win, s.b, n >> p.page_shift, lane);
+          if ((page < 0 || page >= p.num_pages) && lane == 0) atomicExch(p.status, GA_ST_BAD_PAGE);
+          if (lane < C::ATOMS) {
+            const uint32_t dst = (kv ? sV : sK) + st * C::KV_BYTES + lane * SLAB + i * p.box_tok * 128;
+            tma_load_4d(dst, kv ? &vmap : &kmap, full, lane * 128, s.h, n & p.page_mask, page);
+          }
+        }
+      }
+    }
+  } else if (have && warp == 5) {
+    // ---------------------------------------------------------------- MMA issue (one lane)
+    const uint32_t id_qk = instr_desc(TM, TNK, 0), id_pv = instr_desc(TM, 128, 1);
+    auto issue_pv = [&](int t) {
+      const int st = t % C::NKV;
+      wait_or_flag(b_pready + 8 * (t & 1), (t >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
+      wait_or_flag(b_vfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
+      tc_fence_after();
+      if (lane == 0 && !failed) {
+#pragma unroll
+        for (int term = 0; term < 2; ++term) {  // hi term then residual term of P
+          const uint32_t pa = sP + ((t & 1) * 2 + term) * C::P_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < TNK / 32; ++ks) {
+#pragma unroll
+            for (int a = 0; a < C::ATOMS; ++a) {
+              mma_f8(tmem + C::O_COL + a * 128, smem_desc(pa + ks * 32, 16, 1024),
+                     smem_desc(sV + st * C::KV_BYTES + a * SLAB + ks * 32 * 128, SLAB, 1024), id_pv,
+                     (t > 0 || term > 0 || ks > 0) ? 1 : 0);
+            }
+          }
+        }
+        mma_commit(b_vempty + 8 * st);
+        mma_commit(b_pfree + 8 * (t & 1));
+      }
+      __syncwarp();
+    };
+    wait_or_flag(b_q, 0, failed, p.status, GA_ST_WAIT_FULL);
+    for (int t = 0; t < n_tiles; ++t) {
+      const int st = t % C::NKV;
+      wait_or_flag(b_kfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
+      if (t >= 2) wait_or_flag(b_sfree + 8 * (t & 1), ((t >> 1) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      tc_fence_after();
+      if (lane == 0 && !failed) {
+#pragma unroll
+        for (int ks = 0; ks < HD / 32; ++ks) {
+          const uint32_t off = (ks >> 2) * SLAB + (ks & 3) * 32;
+          mma_f8(tmem + C::S_COL + (t & 1) * 128, smem_desc(sQ + off, 16, 1024),
+                 smem_desc(sK + st * C::KV_BYTES + off, 16, 1024), id_qk, ks > 0 ? 1 : 0);
+        }
+        mma_commit(b_kempty + 8 * st);
+        mma_commit(b_sfull + 8 * (t & 1));
+      }
+      __syncwarp();
+      if (t >= 1) issue_pv(t - 1);
+    }
+    if (n_tiles > 0) issue_pv(n_tiles - 1);
+  } else if (have && warp < 4) {
+    // ---------------------------------------------------------------- softmax: thread = query row
+    const int r = tid;
+    const int tq = r / p.gqa, hq = r - tq * p.gqa;
+    const bool valid = tq < s.nq;
+    const int pos = valid ? s.pos0 + tq : -1;
+    const int lo_key = p.window_left >= 0 ? pos - p.window_left : -(1 << 30);
+    // Q: this thread's row, rounded to e4m3, into the swizzled A tile
+    {
+      const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1;
+#pragma unroll 1
+      for (int c = 0; c < HD / 16; ++c) {
+        uint4 pk = make_uint4(0, 0, 0, 0);
+        if (valid) {
+          if (p.q_bf16) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + (off + c * 16) * 2);
+            uint4 x = src[0], y = src[1];
+            auto cv = [](uint32_t a, uint32_t b) {
+              return pack_e4m3x4(bf16_bits_to_f32(a & 0xffffu), bf16_bits_to_f32(a >> 16), bf16_bits_to_f32(b & 0xffffu),
+                                 bf16_bits_to_f32(b >> 16));
+            };
+            pk = make_uint4(cv(x.x, x.y), cv(x.z, x.w), cv(y.x, y.y), cv(y.z, y.w));
+          } else {
+            pk = *reinterpret_cast<const uint4*>(p.q + off + c * 16);
+          }
+        }
+        const uint32_t dst = sQ + (c >> 3) * SLAB + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
+                     : "memory");
+      }
+      fence_proxy_async();
+      mbar_arrive(b_q);
+    }
+    const float kds = p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f;
+    const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
+    const float sl2 = p.scale_log2 * kds;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    float m_used = -INFINITY, l = 0.f;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int n0 = (s.t_lo + t) * TNK;
+      const bool need_mask = (n0 + TNK > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
+      wait_or_flag(b_sfull + 8 * (t & 1), (t >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
+      tc_fence_after();
+      const uint32_t s_addr = lane_base + C::S_COL + (t & 1) * 128;
+      // pass 1: row max of the scaled, masked scores
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TNK; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(s_addr + c0, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float x = __uint_as_float(v[j]) * sl2;
+          if (need_mask) {
+            const int col = n0 + c0 + j;
+            x = (col <= pos && col >= lo_key) ? x : -INFINITY;
+          }
+          mx = fmaxf(mx, x);
+        }
+      }
+      float alpha = 1.f;
+      if (mx > m_used + TC_LAZY || (m_used == -INFINITY && mx > -INFINITY)) {
+        alpha = m_used == -INFINITY ? 0.f : ex2(m_used - mx);
+        m_used = mx;
+      }
+      const float mu = m_used == -INFINITY ? 0.f : m_used;
+      const float sh = TC_SHIFT - mu;
+      l *= alpha;
+      // The P buffer of this tile is free once the PV MMAs of tile t-2 are done.
+      if (t >= 2) wait_or_flag(b_pfree + 8 * (t & 1), ((t >> 1) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      // pass 2: P = 2^(s - m + 7) as hi + residual e4m3 terms, straight into the swizzled A tiles
+      const uint32_t p_hi = sP + ((t & 1) * 2) * C::P_BYTES + r * 128, p_lo = p_hi + C::P_BYTES;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TNK; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(s_addr + c0, v);
+        tmem_wait_ld();
+        uint32_t hi[8], lo[8];
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          float e[4], h[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float x = __uint_as_float(v[q4 * 4 + j]) * sl2;
+            if (need_mask) {
+              const int col = n0 + c0 + q4 * 4 + j;
+              x = (col <= pos && col >= lo_key) ? x : -INFINITY;
+            }
+            e[j] = ex2(x + sh);
+            l += e[j];
+            h[j] = __uint_as_float((__float_as_uint(e[j]) + 0x00080000u) & 0xfff00000u);
+          }
+          hi[q4] = pack_e4m3x4(h[0], h[1], h[2], h[3]);
+          lo[q4] = pack_e4m3x4(e[0] - h[0], e[1] - h[1], e[2] - h[2], e[3] - h[3]);
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t chunk = static_cast<uint32_t>(((c0 >> 4) + half) ^ (r & 7)) << 4;
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_hi + chunk), "r"(hi[half * 4]),
+                       "r"(hi[half * 4 + 1]), "r"(hi[half * 4 + 2]), "r"(hi[half * 4 + 3])
+                       : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_lo + chunk), "r"(lo[half * 4]),
+                       "r"(lo[half * 4 + 1]), "r"(lo[half * 4 + 2]), "r"(lo[half * 4 + 3])
+                       : "memory");
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(b_sfree + 8 * (t & 1));
+      // O in tensor memory is rescaled only when some row of this warp moved its max; needs PV of tile t-1 done.
+      if (t >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        wait_or_flag(b_pfree + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        tc_fence_after();
+#pragma unroll 1
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(lane_base + C::O_COL + c0, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+          tmem_st32(lane_base + C::O_COL + c0, v);
+        }
+        tmem_wait_st();
+      }
+      // rows past the end of the sequence in the last tile: V must be finite where P is exactly 0
+      if (n0 + TNK > s.L) {
+        const int st = t % C::NKV;
+        wait_or_flag(b_vfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
+        if (n0 + r >= s.L) {
+#pragma unroll 1
+          for (int c = 0; c < C::ATOMS * 8; ++c) {
+            const uint32_t a = sV + st * C::KV_BYTES + (c >> 3) * SLAB + r * 128 + ((c & 7) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
+          }
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(b_pready + 8 * (t & 1));
+    }
+    // ---- epilogue: O / l
+    if (n_tiles > 0) {
+      wait_or_flag(b_pfree + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      tc_fence_after();
+    }
+    const bool bad = __any_sync(0xffffffffu, failed);  // tensor-memory loads are warp-collective
+    const float inv = l > 0.f ? vds / l : 0.f;
+    const long long ooff = static_cast<long long>(s.q0 + tq) * p.o_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.o_s1;
+#pragma unroll 1
+    for (int c0 = 0; c0 < HD; c0 += 32) {
+      uint32_t v[32];
+      if (n_tiles > 0 && !bad) {
+        tmem_ld32(lane_base + C::O_COL + c0, v);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0u;
+      }
+      if (valid) {
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + ooff + c0;
+#pragma unroll
+        for (int q8 = 0; q8 < 4; ++q8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[q8 * 8 + 2 * j]) * inv,
+                                                      __uint_as_float(v[q8 * 8 + 2 * j + 1]) * inv);
+            w[j] = *reinterpret_cast<uint32_t*>(&b2);
+          }
+          *reinterpret_cast<uint4*>(dst + q8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+    if (valid && p.lse != nullptr) {
+      p.lse[static_cast<long long>(s.h * p.gqa + hq) * p.total_q + s.q0 + tq] =
+          l > 0.f ? (m_used + lg2(l) - TC_SHIFT) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::TMEM_COLS) : "memory");
+  }
+}
+
+}  // namespace tc
+}  // namespace attn
+}  // namespace ga
