@@ -9,13 +9,13 @@
 //
 // One CTA = 128 query rows (128 / GQA tokens x the GQA heads of one kv head) against the keys they can see,
 // 128 keys per iteration:
-//   * warp 4 (producer) gathers K and V pages with TMA (128-byte swizzle, one box per page and 128-byte head
+//   * warp 8 (producer) gathers K and V pages with TMA (128-byte swizzle, one box per page and 128-byte head
 //     slice, never multicast) into two 2-stage rings;
-//   * warp 5 (one lane) issues the MMAs: S = Q K^T with both operands K-major straight from the swizzled
+//   * warp 9 (one lane) issues the MMAs: S = Q K^T with both operands K-major straight from the swizzled
 //     tiles, and O += P V with P as a K-major A operand from shared memory and V as an MN-major B operand, i.e.
 //     the [token, dim] page layout as it is: no transpose of V anywhere. S (2 x 128 columns, double
 //     buffered) and O (head_dim columns) live in tensor memory;
-//   * warps 0-3 (softmax): thread = query row = tensor-memory lane. Each thread reads its S row with
+//   * warps 0-7 (softmax): two threads per query row (= tensor-memory lane), one per half of the 128 keys. Each reads its S half-row with
 //     tcgen05.ld, does mask / max / exp2 without any cross-thread traffic, writes P as two e4m3 terms
 //     (4 significant bits + residual, so a probability carries ~2^-8 relative error) into swizzled shared
 //     memory, and rescales O in tensor memory only when its running max moved by more than 1.5 in log2 (the
@@ -35,7 +35,7 @@ constexpr int TNK = 128;            // keys per iteration
 constexpr int SLAB = TNK * 128;     // one 128-byte-wide swizzled slab of a 128-row tile
 constexpr float TC_SHIFT = 7.f;     // P = 2^(s - m + 7)
 constexpr float TC_LAZY = 1.5f;     // rescale O only when the row max grew by more than this (log2 units)
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;     // 8 softmax warps, 1 TMA producer warp, 1 MMA issue warp
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   uint64_t d = 0;
@@ -96,12 +96,16 @@ struct TcCfg {
   static constexpr int P_BYTES = SLAB;                // one e4m3 term of P: 128 rows x 128 keys
   static constexpr int KV_BYTES = ATOMS * SLAB;       // one K (or V) tile
   static constexpr int NKV = HD == 128 ? 3 : 2;       // ring depth of each of the K and V rings
-  static constexpr int Q_OFF = 0;
+  // Header (barriers, row-max / row-sum exchange) first, then the 1024-byte aligned operand tiles. At head_dim
+  // 256 this fills the 227 KiB of an SM exactly, so the kernel relies on the 1024-byte alignment it declares for
+  // its dynamic shared memory and checks it at run time.
+  static constexpr int BAR_OFF = 0;
+  static constexpr int X_OFF = 256;                   // row-max exchange [2][2][128] floats (row sums reuse it)
+  static constexpr int Q_OFF = 3072;
   static constexpr int P_OFF = Q_OFF + Q_BYTES;       // [buffer 0|1][hi|lo]
   static constexpr int K_OFF = P_OFF + 4 * P_BYTES;
   static constexpr int V_OFF = K_OFF + NKV * KV_BYTES;
-  static constexpr int BAR_OFF = V_OFF + NKV * KV_BYTES;
-  static constexpr int SMEM_BYTES = 1024 + BAR_OFF + 256;
+  static constexpr int SMEM_BYTES = V_OFF + NKV * KV_BYTES;
   static constexpr int TMEM_COLS = 512;
   static constexpr int S_COL = 0;                     // S buffers at columns 0 and 128
   static constexpr int O_COL = 256;
@@ -123,9 +127,13 @@ __global__ void __launch_bounds__(THREADS, 1)
 attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
                const __grid_constant__ CUtensorMap vmap) {
   using C = TcCfg<HD>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {  // the swizzled tiles need 1024-byte alignment; never seen, but never silently wrong
+    if (threadIdx.x == 0) atomicExch(p.status, GA_ST_BAD_PAGE);
+    return;
+  }
+  uint8_t* gen = smem_raw;
   const uint32_t sQ = base + C::Q_OFF, sP = base + C::P_OFF, sK = base + C::K_OFF, sV = base + C::V_OFF;
   const uint32_t bars = base + C::BAR_OFF;
   // barrier slots
@@ -133,14 +141,18 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   const uint32_t b_kfull = bars + 72, b_kempty = b_kfull + 8 * C::NKV, b_vfull = b_kempty + 8 * C::NKV,
                  b_vempty = b_vfull + 8 * C::NKV;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 72 + 32 * C::NKV);
+  uint32_t* lo_flag = tmem_slot + 2;  // [2]: some row of tile t still needs the residual term of P
+  float* mxbuf = reinterpret_cast<float*>(gen + C::X_OFF);
+  // row sums are exchanged through the parity half of mxbuf that the last tile did not use
+  float* lbuf = mxbuf;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    mbar_init(b_q, 128);
+    mbar_init(b_q, 256);
     for (int i = 0; i < 2; ++i) {
       mbar_init(b_sfull + 8 * i, 1);
-      mbar_init(b_sfree + 8 * i, 128);
-      mbar_init(b_pready + 8 * i, 128);
+      mbar_init(b_sfree + 8 * i, 256);
+      mbar_init(b_pready + 8 * i, 256);
       mbar_init(b_pfree + 8 * i, 1);
     }
     for (int i = 0; i < C::NKV; ++i) {
@@ -149,6 +161,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       mbar_init(b_vfull + 8 * i, 1);
       mbar_init(b_vempty + 8 * i, 1);
     }
+    lo_flag[0] = lo_flag[1] = 0u;
     mbar_fence_init();
   }
   if (warp == 0) {
@@ -167,7 +180,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   const int n_tiles = have ? s.t_hi - s.t_lo : 0;
   bool failed = false;
 
-  if (have && warp == 4) {
+  if (have && warp == 8) {
     // ---------------------------------------------------------------- producer: K and V tiles by TMA
     PtWindow win;
     win.b = -1;
@@ -201,7 +214,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         }
       }
     }
-  } else if (have && warp == 5) {
+  } else if (have && warp == 9) {
     // ---------------------------------------------------------------- MMA issue (one lane)
     const uint32_t id_qk = instr_desc(TM, TNK, 0), id_pv = instr_desc(TM, 128, 1);
     auto issue_pv = [&](int t) {
@@ -210,8 +223,9 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       wait_or_flag(b_vfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
       tc_fence_after();
       if (lane == 0 && !failed) {
-#pragma unroll
-        for (int term = 0; term < 2; ++term) {  // hi term then residual term of P
+        const int terms = atomicExch(lo_flag + (t & 1), 0u) ? 2 : 1;
+#pragma unroll 1
+        for (int term = 0; term < terms; ++term) {  // hi term, then the residual term while some row needs it
           const uint32_t pa = sP + ((t & 1) * 2 + term) * C::P_BYTES;
 #pragma unroll
           for (int ks = 0; ks < TNK / 32; ++ks) {
@@ -248,18 +262,20 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       if (t >= 1) issue_pv(t - 1);
     }
     if (n_tiles > 0) issue_pv(n_tiles - 1);
-  } else if (have && warp < 4) {
-    // ---------------------------------------------------------------- softmax: thread = query row
-    const int r = tid;
+  } else if (have && warp < 8) {
+    // ---------------------------------------------------------------- softmax: two threads per query row
+    // thread (r, hf): row r = tensor-memory lane, key columns [64 hf, 64 hf + 64) of every tile and the
+    // matching half of the output dims.
+    const int r = tid & 127, hf = tid >> 7;
     const int tq = r / p.gqa, hq = r - tq * p.gqa;
     const bool valid = tq < s.nq;
+    const bool warp_live = (warp & 3) * 32 < s.nq * p.gqa;  // some row of this warp is a real query row
     const int pos = valid ? s.pos0 + tq : -1;
     const int lo_key = p.window_left >= 0 ? pos - p.window_left : -(1 << 30);
-    // Q: this thread's row, rounded to e4m3, into the swizzled A tile
-    {
+    {  // Q: half of this row, rounded to e4m3, into the swizzled A tile
       const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1;
 #pragma unroll 1
-      for (int c = 0; c < HD / 16; ++c) {
+      for (int c = hf * (HD / 32); c < (hf + 1) * (HD / 32); ++c) {
         uint4 pk = make_uint4(0, 0, 0, 0);
         if (valid) {
           if (p.q_bf16) {
@@ -284,75 +300,111 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     const float kds = p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f;
     const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
     const float sl2 = p.scale_log2 * kds;
-    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     float m_used = -INFINITY, l = 0.f;
     for (int t = 0; t < n_tiles; ++t) {
       const int n0 = (s.t_lo + t) * TNK;
+      const int c_base = n0 + hf * 64;
       const bool need_mask = (n0 + TNK > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
       wait_or_flag(b_sfull + 8 * (t & 1), (t >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
       tc_fence_after();
-      const uint32_t s_addr = lane_base + C::S_COL + (t & 1) * 128;
-      // pass 1: row max of the scaled, masked scores
+      const uint32_t s_addr = lane_base + C::S_COL + (t & 1) * 128 + hf * 64;
+      // pass 1: max of this thread's 64 scores (raw scores when the scale is positive and nothing is masked)
       float mx = -INFINITY;
+      if (warp_live) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < TNK; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(s_addr + c0, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float x = __uint_as_float(v[j]) * sl2;
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(s_addr + c0, v);
+          tmem_wait_ld();
           if (need_mask) {
-            const int col = n0 + c0 + j;
-            x = (col <= pos && col >= lo_key) ? x : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = c_base + c0 + j;
+              mx = fmaxf(mx, (col <= pos && col >= lo_key) ? __uint_as_float(v[j]) * sl2 : -INFINITY);
+            }
+          } else if (sl2 > 0.f) {  // max of the raw scores, scaled once
+            float raw = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) raw = fmaxf(raw, __uint_as_float(v[j]));
+            mx = fmaxf(mx, raw * sl2);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]) * sl2);
           }
-          mx = fmaxf(mx, x);
         }
       }
+      // The residual term of P is only needed while a row rests on few keys: with l / 2^7 >= 32 in each half the
+      // row has at least 64 effective keys and the e4m3 rounding of P averages out far below the tolerance.
+      if (valid && l < 32.f * 128.f) atomicOr(lo_flag + (t & 1), 1u);
+      mxbuf[((t & 1) * 2 + hf) * 128 + r] = mx;
+      named_bar_sync(2, 256);
+      mx = fmaxf(mx, mxbuf[((t & 1) * 2 + (hf ^ 1)) * 128 + r]);
+      const bool with_lo = lo_flag[t & 1] != 0u;  // same answer in every softmax thread of the CTA
       float alpha = 1.f;
       if (mx > m_used + TC_LAZY || (m_used == -INFINITY && mx > -INFINITY)) {
         alpha = m_used == -INFINITY ? 0.f : ex2(m_used - mx);
         m_used = mx;
       }
-      const float mu = m_used == -INFINITY ? 0.f : m_used;
-      const float sh = TC_SHIFT - mu;
+      const float sh = TC_SHIFT - (m_used == -INFINITY ? 0.f : m_used);
       l *= alpha;
       // The P buffer of this tile is free once the PV MMAs of tile t-2 are done.
       if (t >= 2) wait_or_flag(b_pfree + 8 * (t & 1), ((t >> 1) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
       // pass 2: P = 2^(s - m + 7) as hi + residual e4m3 terms, straight into the swizzled A tiles
-      const uint32_t p_hi = sP + ((t & 1) * 2) * C::P_BYTES + r * 128, p_lo = p_hi + C::P_BYTES;
+      if (warp_live) {
+        const uint32_t p_hi = sP + ((t & 1) * 2) * C::P_BYTES + r * 128, p_lo = p_hi + C::P_BYTES;
 #pragma unroll 1
-      for (int c0 = 0; c0 < TNK; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(s_addr + c0, v);
-        tmem_wait_ld();
-        uint32_t hi[8], lo[8];
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(s_addr + c0, v);
+          tmem_wait_ld();
+          uint32_t hi[8], lo[8];
+          if (with_lo) {
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          float e[4], h[4];
+            for (int q4 = 0; q4 < 8; ++q4) {
+              float e[4], h[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float x = __uint_as_float(v[q4 * 4 + j]) * sl2;
-            if (need_mask) {
-              const int col = n0 + c0 + q4 * 4 + j;
-              x = (col <= pos && col >= lo_key) ? x : -INFINITY;
+              for (int j = 0; j < 4; ++j) {
+                float x = fmaf(__uint_as_float(v[q4 * 4 + j]), sl2, sh);
+                if (need_mask) {
+                  const int col = c_base + c0 + q4 * 4 + j;
+                  x = (col <= pos && col >= lo_key) ? x : -INFINITY;
+                }
+                e[j] = ex2(x);
+                l += e[j];
+                h[j] = __uint_as_float((__float_as_uint(e[j]) + 0x00080000u) & 0xfff00000u);
+              }
+              hi[q4] = pack_e4m3x4(h[0], h[1], h[2], h[3]);
+              lo[q4] = pack_e4m3x4(e[0] - h[0], e[1] - h[1], e[2] - h[2], e[3] - h[3]);
             }
-            e[j] = ex2(x + sh);
-            l += e[j];
-            h[j] = __uint_as_float((__float_as_uint(e[j]) + 0x00080000u) & 0xfff00000u);
-          }
-          hi[q4] = pack_e4m3x4(h[0], h[1], h[2], h[3]);
-          lo[q4] = pack_e4m3x4(e[0] - h[0], e[1] - h[1], e[2] - h[2], e[3] - h[3]);
-        }
+          } else {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const uint32_t chunk = static_cast<uint32_t>(((c0 >> 4) + half) ^ (r & 7)) << 4;
-          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_hi + chunk), "r"(hi[half * 4]),
-                       "r"(hi[half * 4 + 1]), "r"(hi[half * 4 + 2]), "r"(hi[half * 4 + 3])
-                       : "memory");
-          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_lo + chunk), "r"(lo[half * 4]),
-                       "r"(lo[half * 4 + 1]), "r"(lo[half * 4 + 2]), "r"(lo[half * 4 + 3])
-                       : "memory");
+            for (int q4 = 0; q4 < 8; ++q4) {
+              float e[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float x = fmaf(__uint_as_float(v[q4 * 4 + j]), sl2, sh);
+                if (need_mask) {
+                  const int col = c_base + c0 + q4 * 4 + j;
+                  x = (col <= pos && col >= lo_key) ? x : -INFINITY;
+                }
+                e[j] = ex2(x);
+                l += e[j];
+              }
+              hi[q4] = pack_e4m3x4(e[0], e[1], e[2], e[3]);
+            }
+          }
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const uint32_t chunk = static_cast<uint32_t>((hf * 4 + (c0 >> 4) + half) ^ (r & 7)) << 4;
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_hi + chunk), "r"(hi[half * 4]),
+                         "r"(hi[half * 4 + 1]), "r"(hi[half * 4 + 2]), "r"(hi[half * 4 + 3])
+                         : "memory");
+            if (with_lo)
+              asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_lo + chunk), "r"(lo[half * 4]),
+                           "r"(lo[half * 4 + 1]), "r"(lo[half * 4 + 2]), "r"(lo[half * 4 + 3])
+                           : "memory");
+          }
         }
       }
       tc_fence_before();
@@ -362,13 +414,13 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         wait_or_flag(b_pfree + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
         tc_fence_after();
 #pragma unroll 1
-        for (int c0 = 0; c0 < HD; c0 += 32) {
+        for (int c0 = 0; c0 < HD / 2; c0 += 32) {
           uint32_t v[32];
-          tmem_ld32(lane_base + C::O_COL + c0, v);
+          tmem_ld32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
           tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-          tmem_st32(lane_base + C::O_COL + c0, v);
+          tmem_st32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
         }
         tmem_wait_st();
       }
@@ -378,7 +430,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         wait_or_flag(b_vfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
         if (n0 + r >= s.L) {
 #pragma unroll 1
-          for (int c = 0; c < C::ATOMS * 8; ++c) {
+          for (int c = hf * C::ATOMS * 4; c < (hf + 1) * C::ATOMS * 4; ++c) {
             const uint32_t a = sV + st * C::KV_BYTES + (c >> 3) * SLAB + r * 128 + ((c & 7) << 4);
             asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
           }
@@ -388,19 +440,24 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       tc_fence_before();
       mbar_arrive(b_pready + 8 * (t & 1));
     }
-    // ---- epilogue: O / l
+    // ---- epilogue: O / l, each thread one half of the output dims of its row
+    lbuf += (n_tiles & 1) * 256;
+    lbuf[hf * 128 + r] = l;
+    named_bar_sync(2, 256);
+    l += lbuf[(hf ^ 1) * 128 + r];
     if (n_tiles > 0) {
       wait_or_flag(b_pfree + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
       tc_fence_after();
     }
     const bool bad = __any_sync(0xffffffffu, failed);  // tensor-memory loads are warp-collective
     const float inv = l > 0.f ? vds / l : 0.f;
-    const long long ooff = static_cast<long long>(s.q0 + tq) * p.o_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.o_s1;
+    const long long ooff = static_cast<long long>(s.q0 + tq) * p.o_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.o_s1 +
+                           hf * (HD / 2);
 #pragma unroll 1
-    for (int c0 = 0; c0 < HD; c0 += 32) {
+    for (int c0 = 0; c0 < HD / 2; c0 += 32) {
       uint32_t v[32];
       if (n_tiles > 0 && !bad) {
-        tmem_ld32(lane_base + C::O_COL + c0, v);
+        tmem_ld32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
         tmem_wait_ld();
       } else {
 #pragma unroll
@@ -421,7 +478,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         }
       }
     }
-    if (valid && p.lse != nullptr) {
+    if (valid && hf == 0 && p.lse != nullptr) {
       p.lse[static_cast<long long>(s.h * p.gqa + hq) * p.total_q + s.q0 + tq] =
           l > 0.f ? (m_used + lg2(l) - TC_SHIFT) * 0.6931471805599453f : -INFINITY;
     }

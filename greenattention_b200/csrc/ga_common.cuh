@@ -18,6 +18,9 @@ enum : int { GA_ST_OK = 0, GA_ST_WAIT_FULL = 1, GA_ST_WAIT_EMPTY = 2, GA_ST_BAD_
 // hardware-defined interval, so this bounds a stuck wait to seconds, after which the kernel records
 // where it gave up and returns instead of spinning forever.
 constexpr uint32_t kMaxPolls = 1u << 22;
+// Upper bound (ns) a single try_wait may keep the thread suspended before it polls again: waiting warps then
+// take almost no issue slots from the warps that compute.
+constexpr uint32_t kSuspendHintNs = 20000;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -39,10 +42,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
