@@ -187,6 +187,8 @@ def bench_attn_extra(dev, hbm_gbs, steps=5):
     from greenattention_b200 import attn_decode
 
     out = {}
+    fp8_peak = attn_decode.fp8_tensor_peak_tflops(dev)
+    out["fp8_tensor_peak_tflops"] = {"value": fp8_peak, "how": "tcgen05 e4m3 issue loop on every SM, measured in this run"}
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
 
     def timed(kw, select):
@@ -223,9 +225,42 @@ def bench_attn_extra(dev, hbm_gbs, steps=5):
         else:
             fl = W.attn_flops(kw)
             out[name] = {"workload": f"C4 extend: B=8, 2048 new on 16k prefix, QH16/KVH8, hd256, window={window}",
-                         "us_per_call": ms * 1e3, "tflops": fl / ms / 1e9, "flops": fl}
+                         "us_per_call": ms * 1e3, "tflops": fl / ms / 1e9, "flops": fl,
+                         "frac_of_fp8_peak": fl / ms / 1e9 / fp8_peak}
         del kw
     return out
+
+
+def bench_long_context(dev, rank, world, steps=20, total_tokens=1 << 20):
+    """One decode step of a single 1M-token sequence whose KV range is split across the ranks: local split-KV
+    decode on the shard, NCCL all-gather of the packed (O, LSE) partials, local merge. Max over ranks."""
+    import torch.distributed as dist
+
+    from greenattention_b200 import kv_shard
+
+    lo, hi = kv_shard.shard_ranges(total_tokens, world, 64)[rank]
+    kw = W.make_paged_case([hi - lo], [1], 64, q_heads=64, kv_heads=8, head_dim=128, seed=11 + rank, device=dev,
+                           kv_std=0.5, descale="rand", descale_range=(0.5, 2.0), extra_pages=8, return_lse=True)
+    for name in ("q", "k_descale", "v_descale"):  # the request's query and scales are the same on every rank
+        dist.broadcast(kw[name], 0)
+    for _ in range(3):
+        kv_shard.decode_kv_sharded(kw)
+    dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        out = kv_shard.decode_kv_sharded(kw)
+    e.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / steps], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = t.item() * 1e3
+    local_bytes = (hi - lo) * 2048
+    return {"workload": f"one {total_tokens}-token sequence, KV range split over {world} GPUs, QH64/KVH8, hd128, page 64",
+            "us_per_call": us, "kv_bytes_per_gpu": local_bytes, "aggregate_tbps": total_tokens * 2048 / us / 1e6,
+            "exchange": "one NCCL all-gather of 33 KB per rank + local merge kernel", "finite": bool(torch.isfinite(out.float()).all())}
 
 
 def main():
@@ -346,8 +381,12 @@ def main():
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": hbm_gbs, "unit": "GB/s",
                          "frac": per_gpu_gbs / hbm_gbs, "peak_kind": f"{peak_kind} copy bandwidth",
-                         "frac_of_8TBps_nominal": per_gpu_gbs / 8000.0, "traffic": None,
-                         "kernel": "attn_rows_kernel<128,1,4,0> (+ combine, inside the same events)"},
+                         "frac_of_8TBps_nominal": per_gpu_gbs / 8000.0,
+                         # DRAM bytes per launch: ncu capture of the same kernel at batch 16 read+wrote 1.0125 x
+                         # its algorithmic bytes (profiles/attn_rows_decode.md); scaled by the tokens of this launch
+                         "traffic": int(nbytes * 1.0125),
+                         "kernel": "attn_rows_kernel<128,1,3,1,0,true,6,1,2> (+ attn_combine_kernel, ~1.4 % of "
+                                   "the call, inside the same events)"},
         }
         if not args.no_gdn:
             try:
@@ -356,7 +395,7 @@ def main():
                 line["gdn"] = {"error": repr(exc)}
         if args.extra:
             try:
-                del kw, call
+                kw = call = None
                 torch.cuda.empty_cache()
                 line["attn_extra"] = bench_attn_extra(dev, hbm_gbs)
             except Exception as exc:  # noqa: BLE001
@@ -364,6 +403,17 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             val, cores, sample, _ = cpu_oracle_sample(32, seed=7)
             line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+    long_ctx = None
+    if world > 1:
+        try:
+            kw = call = None
+            torch.cuda.empty_cache()
+            long_ctx = bench_long_context(dev, rank, world)
+        except Exception as exc:  # noqa: BLE001
+            long_ctx = {"error": repr(exc)}
+    if rank == 0:
+        if long_ctx is not None:
+            line["long_context"] = long_ctx
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

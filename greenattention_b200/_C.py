@@ -17,7 +17,7 @@ ABI_VERSION = 1
 
 EXPORTS = (
     "ga_init", "ga_attn_workspace_bytes", "ga_attn_decode", "ga_attn_extend", "ga_attn_decode_noalloc", "ga_attn_merge",
-    "ga_gdn_recurrent", "ga_last_launch_count", "ga_attn_workspace_status", "ga_last_error",
+    "ga_gdn_recurrent", "ga_fp8_tensor_peak", "ga_last_launch_count", "ga_attn_workspace_status", "ga_last_error",
     "ga_abi_version", "ga_sm_count",
 )
 
@@ -98,6 +98,8 @@ def lib() -> ctypes.CDLL:
             fn = getattr(handle, name)
             fn.argtypes = [POINTER(ptype), c_void_p]
             fn.restype = c_int
+        handle.ga_fp8_tensor_peak.argtypes = [c_void_p, c_void_p, POINTER(c_float)]
+        handle.ga_fp8_tensor_peak.restype = c_int
         handle.ga_last_launch_count.argtypes = []
         handle.ga_last_launch_count.restype = c_int
         handle.ga_attn_workspace_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]

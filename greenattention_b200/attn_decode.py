@@ -92,6 +92,18 @@ def workspace_status(device: torch.device) -> int:
     return val.value
 
 
+def fp8_tensor_peak_tflops(device: Union[torch.device, None] = None) -> float:
+    """Dense FP8 tensor-core peak of the device (TFLOP/s), measured with a tcgen05 issue loop."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ensure_ready(dev)
+    val = ctypes.c_float(0.0)
+    _C.check(
+        _C.lib().ga_fp8_tensor_peak(workspace(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream, ctypes.byref(val)),
+        "ga_fp8_tensor_peak",
+    )
+    return float(val.value)
+
+
 def _prewarm(backend) -> None:
     ensure_ready()
 

@@ -489,6 +489,35 @@ int ga_gdn_recurrent(const GaGdnParams* g, void* stream) {
   return 0;
 }
 
+int ga_fp8_tensor_peak(void* status_word, void* stream, float* tflops) {
+  int dev;
+  if (current_device(&dev)) return 1;
+  if (!status_word || !tflops) return fail("null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  static bool attr_set[64] = {false};
+  if (!attr_set[dev]) {
+    GA_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(ga::attn::tc::fp8_peak_kernel),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 49152));
+    attr_set[dev] = true;
+  }
+  const int sm = g_dev[dev].sm_count, iters = 100000;
+  cudaEvent_t e0, e1;
+  GA_CUDA(cudaEventCreate(&e0));
+  GA_CUDA(cudaEventCreate(&e1));
+  ga::attn::tc::fp8_peak_kernel<<<sm, 128, 49152, st>>>(1000, static_cast<int*>(status_word));
+  GA_CUDA(cudaEventRecord(e0, st));
+  ga::attn::tc::fp8_peak_kernel<<<sm, 128, 49152, st>>>(iters, static_cast<int*>(status_word));
+  GA_CUDA(cudaEventRecord(e1, st));
+  GA_CUDA(cudaEventSynchronize(e1));
+  float ms = 0.f;
+  GA_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+  GA_CUDA(cudaEventDestroy(e0));
+  GA_CUDA(cudaEventDestroy(e1));
+  *tflops = static_cast<float>(2.0 * 128 * 256 * 32 * static_cast<double>(iters) * sm / (ms * 1e-3) / 1e12);
+  g_launches = 2;
+  return 0;
+}
+
 int ga_attn_workspace_status(const void* workspace, void* stream, int* status) {
   if (!workspace || !status) return fail("null pointer");
   GA_CUDA(cudaMemcpyAsync(status, workspace, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));

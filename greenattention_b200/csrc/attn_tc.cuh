@@ -490,6 +490,47 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   }
 }
 
+// Issue-rate probe: every SM issues `iters` e4m3 MMAs (M 128, N 256, K 32) on zeroed operands and waits for
+// them once. Gives the dense FP8 tensor peak of the device the extend kernel is measured against.
+__global__ void __launch_bounds__(128) fp8_peak_kernel(int iters, int* status) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t slot;
+  const uint32_t base = smem_u32(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  for (int i = tid; i < 49152 / 4; i += 128) reinterpret_cast<uint32_t*>(smem_raw)[i] = 0u;
+  if (tid == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    mbar_fence_init();
+  }
+  fence_proxy_async();
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = slot;
+  if (tid == 0 && (base & 1023u) == 0) {
+    const uint32_t idesc = instr_desc(128, 256, 0);
+    for (int it = 0; it < iters; ++it) {
+      const int ks = it & 3;
+      mma_f8(tmem + (it & 1) * 256, smem_desc(base + ks * 32, 16, 1024), smem_desc(base + 16384 + ks * 32, 16, 1024),
+             idesc, 1);
+    }
+    mma_commit(smem_u32(&bar));
+  } else if (tid == 0) {
+    mbar_arrive(smem_u32(&bar));
+    atomicExch(status, GA_ST_BAD_PAGE);
+  }
+  if (!mbar_wait(smem_u32(&bar), 0) && tid == 0) atomicExch(status, GA_ST_WAIT_TMEM);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+}
+
 }  // namespace tc
 }  // namespace attn
 }  // namespace ga

@@ -145,6 +145,13 @@ int ga_last_launch_count(void);
  * out or a page id was out of range). Synchronises `stream`. */
 int ga_attn_workspace_status(const void* workspace, void* stream, int* status);
 
+/* Measures the dense FP8 (e4m3) tensor-core issue rate of the current device with a loop of tcgen05 MMAs on
+ * zeroed shared-memory operands (M 128, N 256, K 32 per instruction, every SM busy): the denominator the extend
+ * kernel's tensor roofline is quoted against. `status_word` is any 4-byte device location that receives a
+ * non-zero value if a bounded wait runs out (a decode workspace header will do). Synchronises `stream`.
+ * No counterpart in the reference (its benches quote a data-sheet peak, bench/bench_attn_extend.py:104). */
+int ga_fp8_tensor_peak(void* status_word, void* stream, float* tflops);
+
 const char* ga_last_error(void);
 int ga_abi_version(void);
 int ga_sm_count(int device);
