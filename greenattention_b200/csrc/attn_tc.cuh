@@ -309,31 +309,36 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       wait_or_flag(b_sfull + 8 * (t & 1), (t >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
       tc_fence_after();
       const uint32_t s_addr = lane_base + C::S_COL + (t & 1) * 128 + hf * 64;
-      // pass 1: max of this thread's 64 scores (raw scores when the scale is positive and nothing is masked)
+      // This thread's 64 scores are read from tensor memory once and stay in registers for both passes.
+      uint32_t v[64];
       float mx = -INFINITY;
       if (warp_live) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < 64; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(s_addr + c0, v);
-          tmem_wait_ld();
-          if (need_mask) {
+        tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+        tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+        tmem_wait_ld();
+        // pass 1: row max with four independent running maxima (no 64-long dependency chain)
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (need_mask) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = c_base + c0 + j;
-              mx = fmaxf(mx, (col <= pos && col >= lo_key) ? __uint_as_float(v[j]) * sl2 : -INFINITY);
-            }
-          } else if (sl2 > 0.f) {  // max of the raw scores, scaled once
-            float raw = -INFINITY;
+          for (int j = 0; j < 64; ++j) {
+            const int col = c_base + j;
+            const float x = (col <= pos && col >= lo_key) ? __uint_as_float(v[j]) * sl2 : -INFINITY;
+            v[j] = __float_as_uint(x);  // keep the masked, scaled score
+            m4[j & 3] = fmaxf(m4[j & 3], x);
+          }
+        } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) raw = fmaxf(raw, __uint_as_float(v[j]));
-            mx = fmaxf(mx, raw * sl2);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]) * sl2);
+          for (int j = 0; j < 64; ++j) {
+            const float x = __uint_as_float(v[j]) * sl2;
+            v[j] = __float_as_uint(x);
+            m4[j & 3] = fmaxf(m4[j & 3], x);
           }
         }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
+      // S has been read: the buffer may take the scores of tile t + 2
+      tc_fence_before();
+      mbar_arrive(b_sfree + 8 * (t & 1));
       // The residual term of P is only needed while a row rests on few keys: with l / 2^7 >= 32 in each half the
       // row has at least 64 effective keys and the e4m3 rounding of P averages out far below the tolerance.
       if (valid && l < 32.f * 128.f) atomicOr(lo_flag + (t & 1), 1u);
@@ -350,65 +355,40 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       l *= alpha;
       // The P buffer of this tile is free once the PV MMAs of tile t-2 are done.
       if (t >= 2) wait_or_flag(b_pfree + 8 * (t & 1), ((t >> 1) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
-      // pass 2: P = 2^(s - m + 7) as hi + residual e4m3 terms, straight into the swizzled A tiles
+      // pass 2: P = 2^(s - m + 7), e4m3 (plus the residual term while needed), into the swizzled A tiles
       if (warp_live) {
         const uint32_t p_hi = sP + ((t & 1) * 2) * C::P_BYTES + r * 128, p_lo = p_hi + C::P_BYTES;
-#pragma unroll 1
-        for (int c0 = 0; c0 < 64; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(s_addr + c0, v);
-          tmem_wait_ld();
-          uint32_t hi[8], lo[8];
-          if (with_lo) {
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int q4 = 0; q4 < 8; ++q4) {
-              float e[4], h[4];
+        for (int c16 = 0; c16 < 4; ++c16) {  // 16 keys = one 16-byte chunk of the P row
+          uint32_t hi[4], lo[4];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float x = fmaf(__uint_as_float(v[q4 * 4 + j]), sl2, sh);
-                if (need_mask) {
-                  const int col = c_base + c0 + q4 * 4 + j;
-                  x = (col <= pos && col >= lo_key) ? x : -INFINITY;
-                }
-                e[j] = ex2(x);
-                l += e[j];
-                h[j] = __uint_as_float((__float_as_uint(e[j]) + 0x00080000u) & 0xfff00000u);
-              }
+          for (int q4 = 0; q4 < 4; ++q4) {
+            float e[4], h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              e[j] = ex2(__uint_as_float(v[c16 * 16 + q4 * 4 + j]) + sh);
+              l4[j] += e[j];
+              if (with_lo) h[j] = __uint_as_float((__float_as_uint(e[j]) + 0x00080000u) & 0xfff00000u);
+            }
+            if (with_lo) {
               hi[q4] = pack_e4m3x4(h[0], h[1], h[2], h[3]);
               lo[q4] = pack_e4m3x4(e[0] - h[0], e[1] - h[1], e[2] - h[2], e[3] - h[3]);
-            }
-          } else {
-#pragma unroll
-            for (int q4 = 0; q4 < 8; ++q4) {
-              float e[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float x = fmaf(__uint_as_float(v[q4 * 4 + j]), sl2, sh);
-                if (need_mask) {
-                  const int col = c_base + c0 + q4 * 4 + j;
-                  x = (col <= pos && col >= lo_key) ? x : -INFINITY;
-                }
-                e[j] = ex2(x);
-                l += e[j];
-              }
+            } else {
               hi[q4] = pack_e4m3x4(e[0], e[1], e[2], e[3]);
             }
           }
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const uint32_t chunk = static_cast<uint32_t>((hf * 4 + (c0 >> 4) + half) ^ (r & 7)) << 4;
-            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_hi + chunk), "r"(hi[half * 4]),
-                         "r"(hi[half * 4 + 1]), "r"(hi[half * 4 + 2]), "r"(hi[half * 4 + 3])
+          const uint32_t chunk = static_cast<uint32_t>((hf * 4 + c16) ^ (r & 7)) << 4;
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_hi + chunk), "r"(hi[0]), "r"(hi[1]),
+                       "r"(hi[2]), "r"(hi[3])
+                       : "memory");
+          if (with_lo)
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_lo + chunk), "r"(lo[0]), "r"(lo[1]),
+                         "r"(lo[2]), "r"(lo[3])
                          : "memory");
-            if (with_lo)
-              asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_lo + chunk), "r"(lo[half * 4]),
-                           "r"(lo[half * 4 + 1]), "r"(lo[half * 4 + 2]), "r"(lo[half * 4 + 3])
-                           : "memory");
-          }
         }
+        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       }
-      tc_fence_before();
-      mbar_arrive(b_sfree + 8 * (t & 1));
       // O in tensor memory is rescaled only when some row of this warp moved its max; needs PV of tile t-1 done.
       if (t >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
         wait_or_flag(b_pfree + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
