@@ -134,6 +134,14 @@ const AttnInstance* extend_tc_instance(int hd) {
   return hd == 128 ? &e128 : &e256;
 }
 
+// The tcgen05 kernel wants TMA-sized pages and 16-byte aligned q / out rows.
+bool tc_aligned(const GaAttnParams* a, const ga::attn::AttnDev& d) {
+  const uintptr_t qa = reinterpret_cast<uintptr_t>(a->q), oa = reinterpret_cast<uintptr_t>(a->out);
+  const int qel = a->q_is_bf16 ? 8 : 16;
+  return d.use_tma && qa % 16 == 0 && oa % 16 == 0 && a->q_stride_tok % qel == 0 && a->q_stride_head % qel == 0 &&
+         a->o_stride_tok % 8 == 0 && a->o_stride_head % 8 == 0;
+}
+
 int set_smem(const AttnInstance& k) {
   GA_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(k.fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                k.smem));
@@ -320,8 +328,21 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
   d.ws_o = reinterpret_cast<float*>(ws + kWsHeader + ws_prefix_bytes(a->batch) + ws_lse_bytes(sm));
   d.max_q = a->max_seqlen_q;
   d.bq = 0;
-  const AttnInstance* k = decode_instance(a->head_dim, rows);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Speculative verify (more than 16 rows per kv head) with enough (request, kv head) pairs to fill the SMs runs
+  // on the tcgen05 kernel, one CTA per pair; short batches and long contexts keep the split-KV kernel, which
+  // balances tiles across all SMs whatever the batch.
+  if (rows > 16 && !a->out_is_f32 && tc_aligned(a, d) && a->batch * a->kv_heads >= sm) {
+    d.bq = ga::attn::MAX_ROWS / d.gqa;
+    d.max_q = 1 << 30;
+    const AttnInstance* tk = extend_tc_instance(a->head_dim);
+    dim3 tgrid(static_cast<unsigned>(a->total_q / d.bq + a->batch), a->kv_heads);
+    tk->fn<<<tgrid, tk->threads, tk->smem, st>>>(d, kmap, vmap);
+    GA_CUDA(cudaGetLastError());
+    g_launches = 1;
+    return 0;
+  }
+  const AttnInstance* k = decode_instance(a->head_dim, rows);
   const int grid = sm * k->occ;
   k->fn<<<grid, k->threads, k->smem, st>>>(d, kmap, vmap);
   GA_CUDA(cudaGetLastError());
@@ -416,10 +437,7 @@ int ga_attn_extend(const GaAttnParams* a, void* stream) {
   }
   // The tcgen05 kernel wants TMA-sized pages and 16-byte aligned q / out rows; anything else runs on the
   // warp-level MMA kernel.
-  const uintptr_t qa = reinterpret_cast<uintptr_t>(a->q), oa = reinterpret_cast<uintptr_t>(a->out);
-  const int qel = a->q_is_bf16 ? 8 : 16;
-  const bool tc_ok = d.use_tma && qa % 16 == 0 && oa % 16 == 0 && a->q_stride_tok % qel == 0 &&
-                     a->q_stride_head % qel == 0 && a->o_stride_tok % 8 == 0 && a->o_stride_head % 8 == 0;
+  const bool tc_ok = tc_aligned(a, d);
   const AttnInstance* k = tc_ok ? extend_tc_instance(a->head_dim) : extend_instance(a->head_dim);
   dim3 grid(static_cast<unsigned>(blocks), a->kv_heads);
   k->fn<<<grid, k->threads, k->smem, static_cast<cudaStream_t>(stream)>>>(d, kmap, vmap);

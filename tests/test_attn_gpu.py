@@ -255,6 +255,16 @@ def test_graph_replay_changing_split_plan():
         compare(static_out[0], static_out[1], ref_o, ref_lse)
 
 
+@pytest.mark.parametrize("inst,qlen", [(HD128, 5), (HD256, 16), (HD128_G8, 3)])
+def test_verify_large_batch(inst, qlen):
+    # enough (request, kv head) pairs to fill every SM: verify then runs one tcgen05 CTA per pair
+    g = torch.Generator().manual_seed(qlen)
+    lens = torch.randint(qlen, 700, (96,), generator=g).tolist()
+    lens[3], lens[40] = qlen, 0
+    check(W.make_paged_case(lens, [qlen] * 96, 64, seed=70 + qlen, descale="rand", kv_std=0.5, **inst))
+    check(W.make_paged_case(lens, [qlen] * 96, 16, seed=71 + qlen, window=(127, 0), **inst))
+
+
 # ------------------------------------------------------------------ sliding window
 
 
