@@ -9,9 +9,9 @@
 //
 // One CTA = 128 query rows (128 / GQA tokens x the GQA heads of one kv head) against the keys they can see,
 // 128 keys per iteration:
-//   * warp 8 (producer) gathers K and V pages with TMA (128-byte swizzle, one box per page and 128-byte head
-//     slice, never multicast) into two 2-stage rings;
-//   * warp 9 (one lane) issues the MMAs: S = Q K^T with both operands K-major straight from the swizzled
+//   * four producer warps (K / V x even / odd tiles) gather pages with TMA (128-byte swizzle, one box per page
+//     and 128-byte head slice, never multicast) into a K ring and a V ring;
+//   * one lane of the last warp issues the MMAs: S = Q K^T with both operands K-major straight from the swizzled
 //     tiles, and O += P V with P as a K-major A operand from shared memory and V as an MN-major B operand, i.e.
 //     the [token, dim] page layout as it is: no transpose of V anywhere. S (2 x 128 columns, double
 //     buffered) and O (head_dim columns) live in tensor memory;
@@ -35,7 +35,6 @@ constexpr int TNK = 128;            // keys per iteration
 constexpr int SLAB = TNK * 128;     // one 128-byte-wide swizzled slab of a 128-row tile
 constexpr float TC_SHIFT = 7.f;     // P = 2^(s - m + 7)
 constexpr float TC_LAZY = 1.5f;     // rescale O only when the row max grew by more than this (log2 units)
-constexpr int THREADS = 320;     // 8 softmax warps, 1 TMA producer warp, 1 MMA issue warp
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   uint64_t d = 0;
@@ -95,7 +94,7 @@ struct TcCfg {
   static constexpr int Q_BYTES = ATOMS * SLAB;
   static constexpr int P_BYTES = SLAB;                // one e4m3 term of P: 128 rows x 128 keys
   static constexpr int KV_BYTES = ATOMS * SLAB;       // one K (or V) tile
-  static constexpr int NKV = HD == 128 ? 3 : 2;       // ring depth of each of the K and V rings
+  static constexpr int NKV = HD == 128 ? 4 : 2;       // ring depth of each of the K and V rings (even: see producers)
   // Header (barriers, row-max / row-sum exchange) first, then the 1024-byte aligned operand tiles. At head_dim
   // 256 this fills the 227 KiB of an SM exactly, so the kernel relies on the 1024-byte alignment it declares for
   // its dynamic shared memory and checks it at run time.
@@ -122,11 +121,13 @@ __device__ __forceinline__ void wait_or_flag(uint32_t bar, uint32_t parity, bool
   }
 }
 
-template <int HD>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int HD, int NPART>
+__global__ void __launch_bounds__(128 * NPART + 160, 1)
 attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
                const __grid_constant__ CUtensorMap vmap) {
   using C = TcCfg<HD>;
+  constexpr int CW = TNK / NPART;      // key columns per softmax thread
+  constexpr int NSM = 128 * NPART;     // softmax threads
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) {  // the swizzled tiles need 1024-byte alignment; never seen, but never silently wrong
@@ -142,17 +143,16 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
                  b_vempty = b_vfull + 8 * C::NKV;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 72 + 32 * C::NKV);
   uint32_t* lo_flag = tmem_slot + 2;  // [2]: some row of tile t still needs the residual term of P
-  float* mxbuf = reinterpret_cast<float*>(gen + C::X_OFF);
-  // row sums are exchanged through the parity half of mxbuf that the last tile did not use
-  float* lbuf = mxbuf;
+  __nv_bfloat16* mxbuf = reinterpret_cast<__nv_bfloat16*>(gen + C::X_OFF);  // [2][NPART][128], rounded up
+  float* lbuf = reinterpret_cast<float*>(gen + C::X_OFF);  // [NPART][128] row sums, after the last tile
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    mbar_init(b_q, 256);
+    mbar_init(b_q, NSM);
     for (int i = 0; i < 2; ++i) {
       mbar_init(b_sfull + 8 * i, 1);
-      mbar_init(b_sfree + 8 * i, 256);
-      mbar_init(b_pready + 8 * i, 256);
+      mbar_init(b_sfree + 8 * i, NSM);
+      mbar_init(b_pready + 8 * i, NSM);
       mbar_init(b_pfree + 8 * i, 1);
     }
     for (int i = 0; i < C::NKV; ++i) {
@@ -180,41 +180,39 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   const int n_tiles = have ? s.t_hi - s.t_lo : 0;
   bool failed = false;
 
-  if (have && warp == 8) {
-    // ---------------------------------------------------------------- producer: K and V tiles by TMA
+  if (have && warp >= 4 * NPART && warp < 4 * NPART + 4) {
+    // ---------------------------------------------------------------- producers: four warps
+    // One warp's issue loop (barrier wait, expect_tx, page lookup, TMA issue) takes more than a thousand cycles
+    // per tile, so K and V have their own warps, and even and odd tiles too. The ring depth is even, so a stage
+    // is always refilled by the same warp (its parity waits stay within one phase).
+    const int pw = warp - 4 * NPART, kv = pw & 1, par = pw >> 1;
     PtWindow win;
     win.b = -1;
     win.base = win.cur = win.nxt = 0;
-    if (lane == 0) {
-      tma_prefetch_desc(&kmap);
-      tma_prefetch_desc(&vmap);
-    }
+    if (lane == 0) tma_prefetch_desc(kv ? &vmap : &kmap);
     const int nbox = TNK / p.box_tok;
-    for (int t = 0; t < n_tiles; ++t) {
+    for (int t = par; t < n_tiles; t += 2) {
       const int st = t % C::NKV, use = t / C::NKV;
       const int n0 = (s.t_lo + t) * TNK;
       int boxes = 0;
       for (int i = 0; i < nbox; ++i) boxes += (n0 + i * p.box_tok) < s.L;
       const uint32_t bytes = static_cast<uint32_t>(boxes) * p.box_tok * 128 * C::ATOMS;
-#pragma unroll 1
-      for (int kv = 0; kv < 2; ++kv) {
-        const uint32_t full = (kv ? b_vfull : b_kfull) + 8 * st, empty = (kv ? b_vempty : b_kempty) + 8 * st;
-        if (use > 0) wait_or_flag(empty, (use - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
-        if (failed) break;
-        if (lane == 0) mbar_expect_tx(full, bytes);
-        __syncwarp();
-        for (int i = 0; i < boxes; ++i) {
-          const int n = n0 + i * p.box_tok;
-          int page = pt_lookup(p, win, s.b, n >> p.page_shift, lane);
-          if ((page < 0 || page >= p.num_pages) && lane == 0) atomicExch(p.status, GA_ST_BAD_PAGE);
-          if (lane < C::ATOMS) {
-            const uint32_t dst = (kv ? sV : sK) + st * C::KV_BYTES + lane * SLAB + i * p.box_tok * 128;
-            tma_load_4d(dst, kv ? &vmap : &kmap, full, lane * 128, s.h, n & p.page_mask, page);
-          }
+      const uint32_t full = (kv ? b_vfull : b_kfull) + 8 * st, empty = (kv ? b_vempty : b_kempty) + 8 * st;
+      if (use > 0) wait_or_flag(empty, (use - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      if (failed) break;
+      if (lane == 0) mbar_expect_tx(full, bytes);
+      __syncwarp();
+      for (int i = 0; i < boxes; ++i) {
+        const int n = n0 + i * p.box_tok;
+        int page = pt_lookup(p, win, s.b, n >> p.page_shift, lane);
+        if ((page < 0 || page >= p.num_pages) && lane == 0) atomicExch(p.status, GA_ST_BAD_PAGE);
+        if (lane < C::ATOMS) {
+          const uint32_t dst = (kv ? sV : sK) + st * C::KV_BYTES + lane * SLAB + i * p.box_tok * 128;
+          tma_load_4d(dst, kv ? &vmap : &kmap, full, lane * 128, s.h, n & p.page_mask, page);
         }
       }
     }
-  } else if (have && warp == 9) {
+  } else if (have && warp == 4 * NPART + 4) {
     // ---------------------------------------------------------------- MMA issue (one lane)
     const uint32_t id_qk = instr_desc(TM, TNK, 0), id_pv = instr_desc(TM, 128, 1);
     auto issue_pv = [&](int t) {
@@ -262,11 +260,11 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       if (t >= 1) issue_pv(t - 1);
     }
     if (n_tiles > 0) issue_pv(n_tiles - 1);
-  } else if (have && warp < 8) {
+  } else if (have && warp < 4 * NPART) {
     // ---------------------------------------------------------------- softmax: two threads per query row
     // thread (r, hf): row r = tensor-memory lane, key columns [64 hf, 64 hf + 64) of every tile and the
     // matching half of the output dims.
-    const int r = tid & 127, hf = tid >> 7;
+    const int r = tid & 127, hf = tid >> 7;  // hf: which CW-column part of the row this thread owns
     const int tq = r / p.gqa, hq = r - tq * p.gqa;
     const bool valid = tq < s.nq;
     const bool warp_live = (warp & 3) * 32 < s.nq * p.gqa;  // some row of this warp is a real query row
@@ -275,7 +273,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     {  // Q: half of this row, rounded to e4m3, into the swizzled A tile
       const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1;
 #pragma unroll 1
-      for (int c = hf * (HD / 32); c < (hf + 1) * (HD / 32); ++c) {
+      for (int c = hf * (HD / 16 / NPART); c < (hf + 1) * (HD / 16 / NPART); ++c) {
         uint4 pk = make_uint4(0, 0, 0, 0);
         if (valid) {
           if (p.q_bf16) {
@@ -304,23 +302,23 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     float m_used = -INFINITY, l = 0.f;
     for (int t = 0; t < n_tiles; ++t) {
       const int n0 = (s.t_lo + t) * TNK;
-      const int c_base = n0 + hf * 64;
+      const int c_base = n0 + hf * CW;
       const bool need_mask = (n0 + TNK > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
       wait_or_flag(b_sfull + 8 * (t & 1), (t >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
       tc_fence_after();
-      const uint32_t s_addr = lane_base + C::S_COL + (t & 1) * 128 + hf * 64;
+      const uint32_t s_addr = lane_base + C::S_COL + (t & 1) * 128 + hf * CW;
       // This thread's 64 scores are read from tensor memory once and stay in registers for both passes.
-      uint32_t v[64];
+      uint32_t v[CW];
       float mx = -INFINITY;
       if (warp_live) {
-        tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-        tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+#pragma unroll
+        for (int c0 = 0; c0 < CW; c0 += 32) tmem_ld32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[c0]));
         tmem_wait_ld();
         // pass 1: row max with four independent running maxima (no 64-long dependency chain)
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         if (need_mask) {
 #pragma unroll
-          for (int j = 0; j < 64; ++j) {
+          for (int j = 0; j < CW; ++j) {
             const int col = c_base + j;
             const float x = (col <= pos && col >= lo_key) ? __uint_as_float(v[j]) * sl2 : -INFINITY;
             v[j] = __float_as_uint(x);  // keep the masked, scaled score
@@ -328,7 +326,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 64; ++j) {
+          for (int j = 0; j < CW; ++j) {
             const float x = __uint_as_float(v[j]) * sl2;
             v[j] = __float_as_uint(x);
             m4[j & 3] = fmaxf(m4[j & 3], x);
@@ -341,10 +339,14 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       mbar_arrive(b_sfree + 8 * (t & 1));
       // The residual term of P is only needed while a row rests on few keys: with l / 2^7 >= 32 in each half the
       // row has at least 64 effective keys and the e4m3 rounding of P averages out far below the tolerance.
-      if (valid && l < 32.f * 128.f) atomicOr(lo_flag + (t & 1), 1u);
-      mxbuf[((t & 1) * 2 + hf) * 128 + r] = mx;
-      named_bar_sync(2, 256);
-      mx = fmaxf(mx, mxbuf[((t & 1) * 2 + (hf ^ 1)) * 128 + r]);
+      if (valid && l < (64.f / NPART) * 128.f) atomicOr(lo_flag + (t & 1), 1u);
+      // every part publishes its maximum rounded UP to bf16; all threads of a row then take the same maximum
+      // (a slightly high running max only makes P a little smaller)
+      mxbuf[((t & 1) * NPART + hf) * 128 + r] = __float2bfloat16_ru(mx);
+      named_bar_sync(2, NSM);
+      mx = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < NPART; ++q) mx = fmaxf(mx, __bfloat162float(mxbuf[((t & 1) * NPART + q) * 128 + r]));
       const bool with_lo = lo_flag[t & 1] != 0u;  // same answer in every softmax thread of the CTA
       float alpha = 1.f;
       if (mx > m_used + TC_LAZY || (m_used == -INFINITY && mx > -INFINITY)) {
@@ -360,7 +362,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         const uint32_t p_hi = sP + ((t & 1) * 2) * C::P_BYTES + r * 128, p_lo = p_hi + C::P_BYTES;
         float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c16 = 0; c16 < 4; ++c16) {  // 16 keys = one 16-byte chunk of the P row
+        for (int c16 = 0; c16 < CW / 16; ++c16) {  // 16 keys = one 16-byte chunk of the P row
           uint32_t hi[4], lo[4];
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
@@ -378,7 +380,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
               hi[q4] = pack_e4m3x4(e[0], e[1], e[2], e[3]);
             }
           }
-          const uint32_t chunk = static_cast<uint32_t>((hf * 4 + c16) ^ (r & 7)) << 4;
+          const uint32_t chunk = static_cast<uint32_t>((hf * (CW / 16) + c16) ^ (r & 7)) << 4;
           asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_hi + chunk), "r"(hi[0]), "r"(hi[1]),
                        "r"(hi[2]), "r"(hi[3])
                        : "memory");
@@ -394,13 +396,13 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         wait_or_flag(b_pfree + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
         tc_fence_after();
 #pragma unroll 1
-        for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+        for (int c0 = 0; c0 < HD / NPART; c0 += 32) {
           uint32_t v[32];
-          tmem_ld32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
+          tmem_ld32(lane_base + C::O_COL + hf * (HD / NPART) + c0, v);
           tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-          tmem_st32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
+          tmem_st32(lane_base + C::O_COL + hf * (HD / NPART) + c0, v);
         }
         tmem_wait_st();
       }
@@ -410,7 +412,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         wait_or_flag(b_vfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
         if (n0 + r >= s.L) {
 #pragma unroll 1
-          for (int c = hf * C::ATOMS * 4; c < (hf + 1) * C::ATOMS * 4; ++c) {
+          for (int c = hf * (C::ATOMS * 8 / NPART); c < (hf + 1) * (C::ATOMS * 8 / NPART); ++c) {
             const uint32_t a = sV + st * C::KV_BYTES + (c >> 3) * SLAB + r * 128 + ((c & 7) << 4);
             asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
           }
@@ -421,10 +423,12 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       mbar_arrive(b_pready + 8 * (t & 1));
     }
     // ---- epilogue: O / l, each thread one half of the output dims of its row
-    lbuf += (n_tiles & 1) * 256;
+    named_bar_sync(2, NSM);  // every thread is past its last read of the max buffer, which lbuf overlays
     lbuf[hf * 128 + r] = l;
-    named_bar_sync(2, 256);
-    l += lbuf[(hf ^ 1) * 128 + r];
+    named_bar_sync(2, NSM);
+    l = 0.f;
+#pragma unroll
+    for (int q = 0; q < NPART; ++q) l += lbuf[q * 128 + r];
     if (n_tiles > 0) {
       wait_or_flag(b_pfree + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
       tc_fence_after();
@@ -432,12 +436,12 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     const bool bad = __any_sync(0xffffffffu, failed);  // tensor-memory loads are warp-collective
     const float inv = l > 0.f ? vds / l : 0.f;
     const long long ooff = static_cast<long long>(s.q0 + tq) * p.o_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.o_s1 +
-                           hf * (HD / 2);
+                           hf * (HD / NPART);
 #pragma unroll 1
-    for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+    for (int c0 = 0; c0 < HD / NPART; c0 += 32) {
       uint32_t v[32];
       if (n_tiles > 0 && !bad) {
-        tmem_ld32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
+        tmem_ld32(lane_base + C::O_COL + hf * (HD / NPART) + c0, v);
         tmem_wait_ld();
       } else {
 #pragma unroll
