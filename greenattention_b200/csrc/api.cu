@@ -123,15 +123,14 @@ const AttnInstance* extend_instance(int hd) {
   return hd == 128 ? &e128 : &e256;
 }
 
-template <int HD, int NPART>
+template <int HD>
 AttnInstance make_tc_instance() {
-  return {ga::attn::tc::attn_tc_kernel<HD, NPART>, 128 * NPART + 160, ga::attn::tc::TcCfg<HD>::SMEM_BYTES, 128, 1};
+  return {ga::attn::tc::attn_tc_kernel<HD>, ga::attn::tc::TC_THREADS, ga::attn::tc::TcCfg<HD>::SMEM_BYTES, 128, 1};
 }
-// tcgen05 extend kernel: 128 query rows per CTA, four softmax threads per row (measured faster than two on the
-// full-context extend and on large-batch verify; within 2% on the short-window extend).
+// tcgen05 extend kernel: 128 query rows per CTA, two softmax groups alternating over the key tiles.
 const AttnInstance* extend_tc_instance(int hd) {
-  static const AttnInstance e128 = make_tc_instance<128, 4>();
-  static const AttnInstance e256 = make_tc_instance<256, 4>();
+  static const AttnInstance e128 = make_tc_instance<128>();
+  static const AttnInstance e256 = make_tc_instance<256>();
   return hd == 128 ? &e128 : &e256;
 }
 
@@ -291,10 +290,6 @@ int ga_init(int device) {
     for (int rows : {8, 16, 32, 64, 128})
       if (set_smem(*decode_instance(hd, rows))) return 1;
     if (set_smem(*extend_instance(hd)) || set_smem(*extend_tc_instance(hd))) return 1;
-    {
-      static const AttnInstance g128 = make_tc_instance<128, 4>(), g256 = make_tc_instance<256, 4>();
-      if (set_smem(hd == 128 ? g128 : g256)) return 1;
-    }
   }
   GA_CUDA(cudaSetDevice(prev));
   std::lock_guard<std::mutex> lock(g_mu);

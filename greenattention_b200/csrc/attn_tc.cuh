@@ -57,6 +57,20 @@ __device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same MMA with both descriptors given as (low, high) words. The issuing thread is a single lane whose
+// instruction stream is the limit (about 90 cycles per MMA when each 64-bit descriptor is rebuilt, against
+// 64 cycles of tensor time for M 128, N 128, K 32), so the high words are loop constants and a K step is one
+// 32-bit add on the low word: the 14-bit address field (bytes / 16) never carries into the stride fields for
+// addresses inside the 228 KiB window.
+__device__ __forceinline__ void mma_f8_w(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                         uint32_t idesc, int accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -99,7 +113,7 @@ struct TcCfg {
   // 256 this fills the 227 KiB of an SM exactly, so the kernel relies on the 1024-byte alignment it declares for
   // its dynamic shared memory and checks it at run time.
   static constexpr int BAR_OFF = 0;
-  static constexpr int X_OFF = 256;                   // row-max exchange [2][2][128] floats (row sums reuse it)
+  static constexpr int X_OFF = 256;                   // part maxima [2][2][128] bf16, running max [2][128] f32; row sums overlay both
   static constexpr int Q_OFF = 3072;
   static constexpr int P_OFF = Q_OFF + Q_BYTES;       // [buffer 0|1][hi|lo]
   static constexpr int K_OFF = P_OFF + 4 * P_BYTES;
@@ -121,13 +135,61 @@ __device__ __forceinline__ void wait_or_flag(uint32_t bar, uint32_t parity, bool
   }
 }
 
-template <int HD, int NPART>
-__global__ void __launch_bounds__(128 * NPART + 160, 1)
+// exp2 pass over 32 scores of one row held in registers: P = 2^(v * sl2 + sh) as e4m3 (plus the residual term when
+// LO) into two 16-byte chunks of the swizzled P row(s); returns the sum of the unrounded P. MASK and LO are template
+// parameters so that the common tile (below the diagonal, long row) runs the bare FFMA / EX2 / FADD / CVT sequence.
+template <bool MASK, bool LO>
+__device__ __forceinline__ float exp_chunk32(const uint32_t (&v)[32], float sl2, float sh, int col0, int pos, int lo_key,
+                                             uint32_t p_hi, uint32_t p_lo, uint32_t chunk0, uint32_t rx) {
+  float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c16 = 0; c16 < 2; ++c16) {  // 16 keys = one 16-byte chunk of the P row
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      float e[4], h[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int jj = c16 * 16 + q4 * 4 + j;
+        float x = fmaf(__uint_as_float(v[jj]), sl2, sh);
+        if (MASK) {
+          const int col = col0 + jj;
+          x = (col <= pos && col >= lo_key) ? x : -INFINITY;
+        }
+        e[j] = ex2(x);
+        l4[j] += e[j];
+        if (LO) h[j] = __uint_as_float((__float_as_uint(e[j]) + 0x00080000u) & 0xfff00000u);
+      }
+      if (LO) {
+        hi[q4] = pack_e4m3x4(h[0], h[1], h[2], h[3]);
+        lo[q4] = pack_e4m3x4(e[0] - h[0], e[1] - h[1], e[2] - h[2], e[3] - h[3]);
+      } else {
+        hi[q4] = pack_e4m3x4(e[0], e[1], e[2], e[3]);
+      }
+    }
+    const uint32_t chunk = ((chunk0 + c16) ^ rx) << 4;
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_hi + chunk), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]),
+                 "r"(hi[3])
+                 : "memory");
+    if (LO)
+      asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_lo + chunk), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]),
+                   "r"(lo[3])
+                   : "memory");
+  }
+  return (l4[0] + l4[1]) + (l4[2] + l4[3]);
+}
+
+// Threads: 16 softmax warps (two groups of 8), 4 producer warps, 2 MMA-issuing warps.
+constexpr int TC_SOFTMAX = 512;
+constexpr int TC_GROUP = 256;
+constexpr int TC_THREADS = TC_SOFTMAX + 192;
+
+template <int HD>
+__global__ void __launch_bounds__(TC_THREADS, 1)
 attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
                const __grid_constant__ CUtensorMap vmap) {
   using C = TcCfg<HD>;
-  constexpr int CW = TNK / NPART;      // key columns per softmax thread
-  constexpr int NSM = 128 * NPART;     // softmax threads
+  constexpr int CW = TNK / 2;          // key columns per softmax thread (two threads per row and tile)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) {  // the swizzled tiles need 1024-byte alignment; never seen, but never silently wrong
@@ -137,23 +199,26 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   uint8_t* gen = smem_raw;
   const uint32_t sQ = base + C::Q_OFF, sP = base + C::P_OFF, sK = base + C::K_OFF, sV = base + C::V_OFF;
   const uint32_t bars = base + C::BAR_OFF;
-  // barrier slots
-  const uint32_t b_q = bars, b_sfull = bars + 8, b_sfree = bars + 24, b_pready = bars + 40, b_pfree = bars + 56;
-  const uint32_t b_kfull = bars + 72, b_kempty = b_kfull + 8 * C::NKV, b_vfull = b_kempty + 8 * C::NKV,
+  // barrier slots; the [2] ones are indexed by tile parity = softmax group
+  const uint32_t b_q = bars, b_sfull = bars + 8, b_sfree = bars + 24, b_pready = bars + 40, b_pfree = bars + 56,
+                 b_mpub = bars + 72;
+  const uint32_t b_kfull = bars + 88, b_kempty = b_kfull + 8 * C::NKV, b_vfull = b_kempty + 8 * C::NKV,
                  b_vempty = b_vfull + 8 * C::NKV;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 72 + 32 * C::NKV);
-  uint32_t* lo_flag = tmem_slot + 2;  // [2]: some row of tile t still needs the residual term of P
-  __nv_bfloat16* mxbuf = reinterpret_cast<__nv_bfloat16*>(gen + C::X_OFF);  // [2][NPART][128], rounded up
-  float* lbuf = reinterpret_cast<float*>(gen + C::X_OFF);  // [NPART][128] row sums, after the last tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 88 + 32 * C::NKV);
+  uint32_t* lo_flag = tmem_slot + 2;  // [group][2]: the residual term of P is wanted for the group's tile 2u + g
+  __nv_bfloat16* mxbuf = reinterpret_cast<__nv_bfloat16*>(gen + C::X_OFF);  // [group][part][128], rounded up
+  float* mrun = reinterpret_cast<float*>(gen + C::X_OFF + 1024);            // [group][128] running max after a tile
+  float* lbuf = reinterpret_cast<float*>(gen + C::X_OFF);  // [4][128] row sums, after the last tile (overlay)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    mbar_init(b_q, NSM);
+    mbar_init(b_q, TC_SOFTMAX);
     for (int i = 0; i < 2; ++i) {
       mbar_init(b_sfull + 8 * i, 1);
-      mbar_init(b_sfree + 8 * i, NSM);
-      mbar_init(b_pready + 8 * i, NSM);
+      mbar_init(b_sfree + 8 * i, TC_GROUP);
+      mbar_init(b_pready + 8 * i, TC_GROUP);
       mbar_init(b_pfree + 8 * i, 1);
+      mbar_init(b_mpub + 8 * i, TC_GROUP);
     }
     for (int i = 0; i < C::NKV; ++i) {
       mbar_init(b_kfull + 8 * i, 1);
@@ -161,7 +226,9 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       mbar_init(b_vfull + 8 * i, 1);
       mbar_init(b_vempty + 8 * i, 1);
     }
-    lo_flag[0] = lo_flag[1] = 0u;
+    // the first tile of each group always carries the residual term; later tiles by vote
+    lo_flag[0] = lo_flag[2] = 1u;
+    lo_flag[1] = lo_flag[3] = 0u;
     mbar_fence_init();
   }
   if (warp == 0) {
@@ -180,12 +247,12 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   const int n_tiles = have ? s.t_hi - s.t_lo : 0;
   bool failed = false;
 
-  if (have && warp >= 4 * NPART && warp < 4 * NPART + 4) {
+  if (have && warp >= 16 && warp < 20) {
     // ---------------------------------------------------------------- producers: four warps
     // One warp's issue loop (barrier wait, expect_tx, page lookup, TMA issue) takes more than a thousand cycles
     // per tile, so K and V have their own warps, and even and odd tiles too. The ring depth is even, so a stage
     // is always refilled by the same warp (its parity waits stay within one phase).
-    const int pw = warp - 4 * NPART, kv = pw & 1, par = pw >> 1;
+    const int pw = warp - 16, kv = pw & 1, par = pw >> 1;
     PtWindow win;
     win.b = -1;
     win.base = win.cur = win.nxt = 0;
@@ -212,68 +279,79 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         }
       }
     }
-  } else if (have && warp == 4 * NPART + 4) {
-    // ---------------------------------------------------------------- MMA issue (one lane)
-    const uint32_t id_qk = instr_desc(TM, TNK, 0), id_pv = instr_desc(TM, 128, 1);
-    auto issue_pv = [&](int t) {
-      const int st = t % C::NKV;
-      wait_or_flag(b_pready + 8 * (t & 1), (t >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
-      wait_or_flag(b_vfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
-      tc_fence_after();
-      if (lane == 0 && !failed) {
-        const int terms = atomicExch(lo_flag + (t & 1), 0u) ? 2 : 1;
-#pragma unroll 1
-        for (int term = 0; term < terms; ++term) {  // hi term, then the residual term while some row needs it
-          const uint32_t pa = sP + ((t & 1) * 2 + term) * C::P_BYTES;
-#pragma unroll
-          for (int ks = 0; ks < TNK / 32; ++ks) {
-#pragma unroll
-            for (int a = 0; a < C::ATOMS; ++a) {
-              mma_f8(tmem + C::O_COL + a * 128, smem_desc(pa + ks * 32, 16, 1024),
-                     smem_desc(sV + st * C::KV_BYTES + a * SLAB + ks * 32 * 128, SLAB, 1024), id_pv,
-                     (t > 0 || term > 0 || ks > 0) ? 1 : 0);
-            }
-          }
-        }
-        mma_commit(b_vempty + 8 * st);
-        mma_commit(b_pfree + 8 * (t & 1));
-      }
-      __syncwarp();
-    };
-    wait_or_flag(b_q, 0, failed, p.status, GA_ST_WAIT_FULL);
-    for (int t = 0; t < n_tiles; ++t) {
-      const int st = t % C::NKV;
-      wait_or_flag(b_kfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
-      if (t >= 2) wait_or_flag(b_sfree + 8 * (t & 1), ((t >> 1) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
-      tc_fence_after();
-      if (lane == 0 && !failed) {
+  } else if (have && warp == 20) {
+    // ---------------------------------------------------------------- QK issue: one lane
+    // The two issuing lanes (this one and the PV one) run on their own: the next scores are what a softmax group
+    // waits for once it hands back its S buffer, so they must not queue behind the PV wait. Each lane's
+    // instruction stream is the limit of the tensor pipe here, so descriptors are whole 64-bit registers
+    // prepared before the waits, and a K step is one add.
+    if (lane == 0) {
+      const uint32_t id_qk = instr_desc(TM, TNK, 0);
+      const uint64_t dq = smem_desc(sQ, 16, 1024), dk = smem_desc(sK, 16, 1024);
+      wait_or_flag(b_q, 0, failed, p.status, GA_ST_WAIT_FULL);
+      for (int t = 0; t < n_tiles && !failed; ++t) {
+        const int st = t % C::NKV;
+        const uint64_t kb = dk + static_cast<uint64_t>(st * (C::KV_BYTES >> 4));
+        const uint32_t sd = tmem + C::S_COL + (t & 1) * 128;
+        wait_or_flag(b_kfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
+        if (t >= 2) wait_or_flag(b_sfree + 8 * (t & 1), ((t >> 1) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        if (failed) break;
+        tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < HD / 32; ++ks) {
-          const uint32_t off = (ks >> 2) * SLAB + (ks & 3) * 32;
-          mma_f8(tmem + C::S_COL + (t & 1) * 128, smem_desc(sQ + off, 16, 1024),
-                 smem_desc(sK + st * C::KV_BYTES + off, 16, 1024), id_qk, ks > 0 ? 1 : 0);
+          const uint64_t off = static_cast<uint64_t>(((ks >> 2) * SLAB + (ks & 3) * 32) >> 4);
+          mma_f8(sd, dq + off, kb + off, id_qk, ks > 0 ? 1 : 0);
         }
         mma_commit(b_kempty + 8 * st);
         mma_commit(b_sfull + 8 * (t & 1));
       }
-      __syncwarp();
-      if (t >= 1) issue_pv(t - 1);
     }
-    if (n_tiles > 0) issue_pv(n_tiles - 1);
-  } else if (have && warp < 4 * NPART) {
-    // ---------------------------------------------------------------- softmax: two threads per query row
-    // thread (r, hf): row r = tensor-memory lane, key columns [64 hf, 64 hf + 64) of every tile and the
-    // matching half of the output dims.
-    const int r = tid & 127, hf = tid >> 7;  // hf: which CW-column part of the row this thread owns
+  } else if (have && warp == 21) {
+    // ---------------------------------------------------------------- PV issue: one lane
+    // O += P V with V as an MN-major B operand covering all head dims in one instruction (N = head_dim: at 256
+    // the second 128-dim slab is found through the leading-dimension stride of the descriptor).
+    if (lane == 0) {
+      const uint32_t id_pv = instr_desc(TM, HD, 1);
+      const uint64_t dp = smem_desc(sP, 16, 1024), dv = smem_desc(sV, SLAB, 1024);
+      for (int t = 0; t < n_tiles && !failed; ++t) {
+        const int st = t % C::NKV;
+        const uint64_t vb = dv + static_cast<uint64_t>(st * (C::KV_BYTES >> 4));
+        const uint64_t pb = dp + static_cast<uint64_t>((t & 1) * 2 * (C::P_BYTES >> 4));
+        wait_or_flag(b_pready + 8 * (t & 1), (t >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
+        wait_or_flag(b_vfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
+        if (failed) break;
+        tc_fence_after();
+        const int terms = atomicExch(lo_flag + (t & 1) * 2 + ((t >> 1) & 1), 0u) ? 2 : 1;
+#pragma unroll 1
+        for (int term = 0; term < terms; ++term) {  // hi term, then the residual term while some row needs it
+          const uint64_t pa = pb + static_cast<uint64_t>(term * (C::P_BYTES >> 4));
+#pragma unroll
+          for (int ks = 0; ks < TNK / 32; ++ks)
+            mma_f8(tmem + C::O_COL, pa + static_cast<uint64_t>(ks * 2), vb + static_cast<uint64_t>(ks * (32 * 128 >> 4)), id_pv,
+                   (t > 0 || term > 0 || ks > 0) ? 1 : 0);
+        }
+        mma_commit(b_vempty + 8 * st);
+        mma_commit(b_pfree + 8 * (t & 1));
+      }
+    }
+  } else if (have && warp < 16) {
+    // ---------------------------------------------------------------- softmax: two groups of 256 threads
+    // Group g takes the tiles of parity g (its own S and P buffers), two threads per query row: thread (r, hf) owns
+    // row r = tensor-memory lane, key columns [64 hf, 64 hf + 64) of the tile and the matching part of the output
+    // dims. While one group is in its exp2 pass (the SM's 16 exp2 per clock are the floor of a tile), the other
+    // waits for scores, reads them and finds its row maxima. The running max is one chain over all tiles: a group
+    // takes the value the other group published for the tile before, decides, and publishes its own.
+    const int g = tid >> 8, hf = (tid >> 7) & 1, r = tid & 127;
+    const int part = g * 2 + hf;  // quarter of the head dims this thread loads of Q and stores of O
     const int tq = r / p.gqa, hq = r - tq * p.gqa;
     const bool valid = tq < s.nq;
     const bool warp_live = (warp & 3) * 32 < s.nq * p.gqa;  // some row of this warp is a real query row
     const int pos = valid ? s.pos0 + tq : -1;
     const int lo_key = p.window_left >= 0 ? pos - p.window_left : -(1 << 30);
-    {  // Q: half of this row, rounded to e4m3, into the swizzled A tile
+    {  // Q: a quarter of this row, rounded to e4m3, into the swizzled A tile
       const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1;
 #pragma unroll 1
-      for (int c = hf * (HD / 16 / NPART); c < (hf + 1) * (HD / 16 / NPART); ++c) {
+      for (int c = part * (HD / 64); c < (part + 1) * (HD / 64); ++c) {
         uint4 pk = make_uint4(0, 0, 0, 0);
         if (valid) {
           if (p.q_bf16) {
@@ -299,110 +377,105 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
     const float sl2 = p.scale_log2 * kds;
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    float m_used = -INFINITY, l = 0.f;
-    for (int t = 0; t < n_tiles; ++t) {
+    const uint32_t grp_bar = 2 + g;        // named barrier of this group
+    float m_seen = -INFINITY, l = 0.f;     // l is relative to m_seen
+    for (int t = g; t < n_tiles; t += 2) {
+      const int u = t >> 1;                // this group's iteration: phases of its own barriers
       const int n0 = (s.t_lo + t) * TNK;
       const int c_base = n0 + hf * CW;
       const bool need_mask = (n0 + TNK > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
-      wait_or_flag(b_sfull + 8 * (t & 1), (t >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
+      wait_or_flag(b_sfull + 8 * g, u & 1, failed, p.status, GA_ST_WAIT_FULL);
       tc_fence_after();
-      const uint32_t s_addr = lane_base + C::S_COL + (t & 1) * 128 + hf * CW;
-      // This thread's 64 scores are read from tensor memory once and stay in registers for both passes.
-      uint32_t v[CW];
+      const uint32_t s_addr = lane_base + C::S_COL + g * 128 + hf * CW;
+      // pass 1: row max of the masked, scaled scores, 32 columns at a time (the scores stay in tensor memory)
       float mx = -INFINITY;
       if (warp_live) {
-#pragma unroll
-        for (int c0 = 0; c0 < CW; c0 += 32) tmem_ld32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[c0]));
-        tmem_wait_ld();
-        // pass 1: row max with four independent running maxima (no 64-long dependency chain)
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (need_mask) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < CW; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(s_addr + c0, v);
+          tmem_wait_ld();
+          if (need_mask) {
 #pragma unroll
-          for (int j = 0; j < CW; ++j) {
-            const int col = c_base + j;
-            const float x = (col <= pos && col >= lo_key) ? __uint_as_float(v[j]) * sl2 : -INFINITY;
-            v[j] = __float_as_uint(x);  // keep the masked, scaled score
-            m4[j & 3] = fmaxf(m4[j & 3], x);
-          }
-        } else {
+            for (int j = 0; j < 32; ++j) {
+              const int col = c_base + c0 + j;
+              const float x = (col <= pos && col >= lo_key) ? __uint_as_float(v[j]) : -INFINITY;
+              m4[j & 3] = fmaxf(m4[j & 3], x);
+            }
+          } else {
 #pragma unroll
-          for (int j = 0; j < CW; ++j) {
-            const float x = __uint_as_float(v[j]) * sl2;
-            v[j] = __float_as_uint(x);
-            m4[j & 3] = fmaxf(m4[j & 3], x);
+            for (int j = 0; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
           }
         }
-        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * sl2;  // sl2 > 0; -inf stays -inf
       }
-      // S has been read: the buffer may take the scores of tile t + 2
-      tc_fence_before();
-      mbar_arrive(b_sfree + 8 * (t & 1));
-      // The residual term of P is only needed while a row rests on few keys: with l / 2^7 >= 32 in each half the
-      // row has at least 64 effective keys and the e4m3 rounding of P averages out far below the tolerance.
-      if (valid && l < (64.f / NPART) * 128.f) atomicOr(lo_flag + (t & 1), 1u);
-      // every part publishes its maximum rounded UP to bf16; all threads of a row then take the same maximum
-      // (a slightly high running max only makes P a little smaller)
-      mxbuf[((t & 1) * NPART + hf) * 128 + r] = __float2bfloat16_ru(mx);
-      named_bar_sync(2, NSM);
-      mx = -INFINITY;
-#pragma unroll
-      for (int q = 0; q < NPART; ++q) mx = fmaxf(mx, __bfloat162float(mxbuf[((t & 1) * NPART + q) * 128 + r]));
-      const bool with_lo = lo_flag[t & 1] != 0u;  // same answer in every softmax thread of the CTA
-      float alpha = 1.f;
-      if (mx > m_used + TC_LAZY || (m_used == -INFINITY && mx > -INFINITY)) {
-        alpha = m_used == -INFINITY ? 0.f : ex2(m_used - mx);
-        m_used = mx;
+      // both parts publish their maximum rounded UP to bf16 and take the larger (a slightly high running max
+      // only makes P a little smaller)
+      mxbuf[(g * 2 + hf) * 128 + r] = __float2bfloat16_ru(mx);
+      named_bar_sync(grp_bar, TC_GROUP);
+      mx = fmaxf(__bfloat162float(mxbuf[(g * 2) * 128 + r]), __bfloat162float(mxbuf[(g * 2 + 1) * 128 + r]));
+      // the running max after tile t - 1, from the other group
+      float m_prev = -INFINITY;
+      if (t >= 1) {
+        wait_or_flag(b_mpub + 8 * (g ^ 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
+        m_prev = mrun[(g ^ 1) * 128 + r];
       }
-      const float sh = TC_SHIFT - (m_used == -INFINITY ? 0.f : m_used);
-      l *= alpha;
-      // The P buffer of this tile is free once the PV MMAs of tile t-2 are done.
-      if (t >= 2) wait_or_flag(b_pfree + 8 * (t & 1), ((t >> 1) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      float m_new = m_prev, alpha = 1.f;  // alpha: what O (relative to m_prev) is multiplied by
+      if (mx > m_prev + TC_LAZY || (m_prev == -INFINITY && mx > -INFINITY)) {
+        alpha = m_prev == -INFINITY ? 0.f : ex2(m_prev - mx);
+        m_new = mx;
+      }
+      if (hf == 0) mrun[g * 128 + r] = m_new;
+      mbar_arrive(b_mpub + 8 * g);
+      if (m_new != m_seen) {  // this group's row sum is relative to the max it saw two tiles ago
+        l = m_seen == -INFINITY ? 0.f : l * ex2(m_seen - m_new);
+        m_seen = m_new;
+      }
+      const float sh = TC_SHIFT - (m_new == -INFINITY ? 0.f : m_new);
+      // The P buffer of this group is free once the PV MMAs of tile t-2 are done.
+      if (t >= 2) wait_or_flag(b_pfree + 8 * g, (u - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      const bool with_lo = lo_flag[g * 2 + (u & 1)] != 0u;
       // pass 2: P = 2^(s - m + 7), e4m3 (plus the residual term while needed), into the swizzled A tiles
       if (warp_live) {
-        const uint32_t p_hi = sP + ((t & 1) * 2) * C::P_BYTES + r * 128, p_lo = p_hi + C::P_BYTES;
-        float l4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c16 = 0; c16 < CW / 16; ++c16) {  // 16 keys = one 16-byte chunk of the P row
-          uint32_t hi[4], lo[4];
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            float e[4], h[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              e[j] = ex2(__uint_as_float(v[c16 * 16 + q4 * 4 + j]) + sh);
-              l4[j] += e[j];
-              if (with_lo) h[j] = __uint_as_float((__float_as_uint(e[j]) + 0x00080000u) & 0xfff00000u);
-            }
-            if (with_lo) {
-              hi[q4] = pack_e4m3x4(h[0], h[1], h[2], h[3]);
-              lo[q4] = pack_e4m3x4(e[0] - h[0], e[1] - h[1], e[2] - h[2], e[3] - h[3]);
-            } else {
-              hi[q4] = pack_e4m3x4(e[0], e[1], e[2], e[3]);
-            }
+        const uint32_t p_hi = sP + (g * 2) * C::P_BYTES + r * 128, p_lo = p_hi + C::P_BYTES;
+        float lsum = 0.f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < CW; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(s_addr + c0, v);
+          tmem_wait_ld();
+          const uint32_t chunk0 = static_cast<uint32_t>(hf * (CW / 16) + (c0 >> 4)), rx = static_cast<uint32_t>(r & 7);
+          if (with_lo) {
+            lsum += need_mask ? exp_chunk32<true, true>(v, sl2, sh, c_base + c0, pos, lo_key, p_hi, p_lo, chunk0, rx)
+                              : exp_chunk32<false, true>(v, sl2, sh, c_base + c0, pos, lo_key, p_hi, p_lo, chunk0, rx);
+          } else {
+            lsum += need_mask ? exp_chunk32<true, false>(v, sl2, sh, c_base + c0, pos, lo_key, p_hi, p_lo, chunk0, rx)
+                              : exp_chunk32<false, false>(v, sl2, sh, c_base + c0, pos, lo_key, p_hi, p_lo, chunk0, rx);
           }
-          const uint32_t chunk = static_cast<uint32_t>((hf * (CW / 16) + c16) ^ (r & 7)) << 4;
-          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_hi + chunk), "r"(hi[0]), "r"(hi[1]),
-                       "r"(hi[2]), "r"(hi[3])
-                       : "memory");
-          if (with_lo)
-            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_lo + chunk), "r"(lo[0]), "r"(lo[1]),
-                         "r"(lo[2]), "r"(lo[3])
-                         : "memory");
         }
-        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+        l += lsum;
       }
+      // S has been read for the last time: the buffer may take the scores of tile t + 2
+      tc_fence_before();
+      mbar_arrive(b_sfree + 8 * g);
+      // The residual term of P is only needed while a row rests on few keys: once this thread's share of the row
+      // sum stands for at least 32 keys at the running max, the e4m3 rounding of P averages out far below the
+      // tolerance. The vote is for this group's next tile (read there after the wait for this tile's PV MMAs,
+      // which follow every thread's arrival below).
+      if (valid && l < 32.f * 128.f) atomicOr(lo_flag + g * 2 + ((u + 1) & 1), 1u);
       // O in tensor memory is rescaled only when some row of this warp moved its max; needs PV of tile t-1 done.
       if (t >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        wait_or_flag(b_pfree + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        wait_or_flag(b_pfree + 8 * (g ^ 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
         tc_fence_after();
 #pragma unroll 1
-        for (int c0 = 0; c0 < HD / NPART; c0 += 32) {
+        for (int c0 = 0; c0 < HD / 2; c0 += 32) {
           uint32_t v[32];
-          tmem_ld32(lane_base + C::O_COL + hf * (HD / NPART) + c0, v);
+          tmem_ld32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
           tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-          tmem_st32(lane_base + C::O_COL + hf * (HD / NPART) + c0, v);
+          tmem_st32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
         }
         tmem_wait_st();
       }
@@ -412,7 +485,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         wait_or_flag(b_vfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
         if (n0 + r >= s.L) {
 #pragma unroll 1
-          for (int c = hf * (C::ATOMS * 8 / NPART); c < (hf + 1) * (C::ATOMS * 8 / NPART); ++c) {
+          for (int c = hf * (C::ATOMS * 4); c < (hf + 1) * (C::ATOMS * 4); ++c) {
             const uint32_t a = sV + st * C::KV_BYTES + (c >> 3) * SLAB + r * 128 + ((c & 7) << 4);
             asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
           }
@@ -420,28 +493,30 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       }
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(b_pready + 8 * (t & 1));
+      mbar_arrive(b_pready + 8 * g);
     }
-    // ---- epilogue: O / l, each thread one half of the output dims of its row
-    named_bar_sync(2, NSM);  // every thread is past its last read of the max buffer, which lbuf overlays
-    lbuf[hf * 128 + r] = l;
-    named_bar_sync(2, NSM);
-    l = 0.f;
-#pragma unroll
-    for (int q = 0; q < NPART; ++q) l += lbuf[q * 128 + r];
+    // ---- epilogue: O / l, each thread one quarter of the output dims of its row
+    named_bar_sync(1, TC_SOFTMAX);  // all tiles of both groups are through their max exchange
+    const int g_last = (n_tiles - 1) & 1;
+    const float m_fin = n_tiles > 0 ? mrun[g_last * 128 + r] : -INFINITY;
+    if (m_seen != m_fin) l = m_seen == -INFINITY ? 0.f : l * ex2(m_seen - m_fin);
+    named_bar_sync(1, TC_SOFTMAX);  // the row sums overlay the max buffers
+    lbuf[part * 128 + r] = l;
+    named_bar_sync(1, TC_SOFTMAX);
+    l = (lbuf[r] + lbuf[128 + r]) + (lbuf[256 + r] + lbuf[384 + r]);
     if (n_tiles > 0) {
-      wait_or_flag(b_pfree + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      wait_or_flag(b_pfree + 8 * g_last, ((n_tiles - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
       tc_fence_after();
     }
     const bool bad = __any_sync(0xffffffffu, failed);  // tensor-memory loads are warp-collective
     const float inv = l > 0.f ? vds / l : 0.f;
     const long long ooff = static_cast<long long>(s.q0 + tq) * p.o_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.o_s1 +
-                           hf * (HD / NPART);
+                           part * (HD / 4);
 #pragma unroll 1
-    for (int c0 = 0; c0 < HD / NPART; c0 += 32) {
+    for (int c0 = 0; c0 < HD / 4; c0 += 32) {
       uint32_t v[32];
       if (n_tiles > 0 && !bad) {
-        tmem_ld32(lane_base + C::O_COL + hf * (HD / NPART) + c0, v);
+        tmem_ld32(lane_base + C::O_COL + part * (HD / 4) + c0, v);
         tmem_wait_ld();
       } else {
 #pragma unroll
@@ -462,9 +537,9 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         }
       }
     }
-    if (valid && hf == 0 && p.lse != nullptr) {
+    if (valid && part == 0 && p.lse != nullptr) {
       p.lse[static_cast<long long>(s.h * p.gqa + hq) * p.total_q + s.q0 + tq] =
-          l > 0.f ? (m_used + lg2(l) - TC_SHIFT) * 0.6931471805599453f : -INFINITY;
+          l > 0.f ? (m_fin + lg2(l) - TC_SHIFT) * 0.6931471805599453f : -INFINITY;
     }
   }
   tc_fence_before();
