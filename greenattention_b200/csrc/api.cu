@@ -123,6 +123,25 @@ const AttnInstance* extend_instance(int hd) {
   return hd == 128 ? &e128 : &e256;
 }
 
+// Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor in the
+// stream drains, and orders itself with griddepcontrol.wait (replaces the reference's PDL launch of its
+// combine kernel, csrc/sm90/attn_decode_fp8/launcher.cu:115-128).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <int HD>
 AttnInstance make_tc_instance() {
   return {ga::attn::tc::attn_tc_kernel<HD>, ga::attn::tc::TC_THREADS, ga::attn::tc::TcCfg<HD>::SMEM_BYTES, 128, 1};
@@ -344,12 +363,10 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
   }
   const AttnInstance* k = decode_instance(a->head_dim, rows);
   const int grid = sm * k->occ;
-  k->fn<<<grid, k->threads, k->smem, st>>>(d, kmap, vmap);
-  GA_CUDA(cudaGetLastError());
+  GA_CUDA(launch_pdl(k->fn, dim3(grid), dim3(k->threads), k->smem, st, d, kmap, vmap));
   dim3 cgrid(a->batch, a->kv_heads);
-  if (a->head_dim == 128) ga::attn::attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(d, grid, k->rows);
-  else ga::attn::attn_combine_kernel<256><<<cgrid, 128, 0, st>>>(d, grid, k->rows);
-  GA_CUDA(cudaGetLastError());
+  if (a->head_dim == 128) GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, cgrid, dim3(128), 0, st, d, grid, k->rows));
+  else GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, cgrid, dim3(128), 0, st, d, grid, k->rows));
   g_launches = 2;
   return 0;
 }

@@ -839,6 +839,11 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
     mbar_fence_init();
   }
   __syncthreads();
+  // Programmatic dependent launch: everything above overlapped the tail of the kernel before this one in the
+  // stream; nothing it wrote is read, and nothing it reads is written, before this wait. The combine kernel
+  // that follows may be scheduled from now on (it waits for this whole grid before it reads a partial).
+  grid_dep_wait();
+  grid_dep_launch();
 
   // ---- segment source
   SliceWalker walk;
@@ -1119,7 +1124,8 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
 template <int HD>
 __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant__ AttnDev p, int G, int rows_cap) {
   const int b = blockIdx.x, h = blockIdx.y;
-  grid_dep_wait();
+  grid_dep_wait();    // the whole decode grid has finished and its partials are visible
+  grid_dep_launch();  // the next kernel in the stream may start its own prologue
   SeqInfo si = seq_info(p, b);
   int ql_all = p.cu[b + 1] - p.cu[b];
   if (ql_all <= 0) return;

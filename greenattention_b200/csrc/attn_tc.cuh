@@ -120,8 +120,11 @@ struct TcCfg {
   static constexpr int V_OFF = K_OFF + NKV * KV_BYTES;
   static constexpr int SMEM_BYTES = V_OFF + NKV * KV_BYTES;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int S_COL = 0;                     // S buffers at columns 0 and 128
-  static constexpr int O_COL = 256;
+  // Tensor memory: NS score buffers of 128 columns, then O (head_dim columns). Head dim 128 leaves room for a
+  // third score buffer, so the QK MMAs of tile t + 2 need not wait for the softmax of tile t.
+  static constexpr int NS = HD == 128 ? 3 : 2;
+  static constexpr int S_COL = 0;
+  static constexpr int O_COL = NS * 128;
   static_assert(SMEM_BYTES <= SMEM_OPTIN, "shared memory");
 };
 
@@ -200,11 +203,11 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   const uint32_t sQ = base + C::Q_OFF, sP = base + C::P_OFF, sK = base + C::K_OFF, sV = base + C::V_OFF;
   const uint32_t bars = base + C::BAR_OFF;
   // barrier slots; the [2] ones are indexed by tile parity = softmax group
-  const uint32_t b_q = bars, b_sfull = bars + 8, b_sfree = bars + 24, b_pready = bars + 40, b_pfree = bars + 56,
-                 b_mpub = bars + 72;
-  const uint32_t b_kfull = bars + 88, b_kempty = b_kfull + 8 * C::NKV, b_vfull = b_kempty + 8 * C::NKV,
+  const uint32_t b_q = bars, b_sfull = bars + 8, b_sfree = bars + 32, b_pready = bars + 56, b_pfree = bars + 72,
+                 b_mpub = bars + 88;
+  const uint32_t b_kfull = bars + 104, b_kempty = b_kfull + 8 * C::NKV, b_vfull = b_kempty + 8 * C::NKV,
                  b_vempty = b_vfull + 8 * C::NKV;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 88 + 32 * C::NKV);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 104 + 32 * C::NKV);
   uint32_t* lo_flag = tmem_slot + 2;  // [group][2]: the residual term of P is wanted for the group's tile 2u + g
   __nv_bfloat16* mxbuf = reinterpret_cast<__nv_bfloat16*>(gen + C::X_OFF);  // [group][part][128], rounded up
   float* mrun = reinterpret_cast<float*>(gen + C::X_OFF + 1024);            // [group][128] running max after a tile
@@ -214,11 +217,13 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   if (tid == 0) {
     mbar_init(b_q, TC_SOFTMAX);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(b_sfull + 8 * i, 1);
-      mbar_init(b_sfree + 8 * i, TC_GROUP);
       mbar_init(b_pready + 8 * i, TC_GROUP);
       mbar_init(b_pfree + 8 * i, 1);
       mbar_init(b_mpub + 8 * i, TC_GROUP);
+    }
+    for (int i = 0; i < C::NS; ++i) {
+      mbar_init(b_sfull + 8 * i, 1);
+      mbar_init(b_sfree + 8 * i, TC_GROUP);
     }
     for (int i = 0; i < C::NKV; ++i) {
       mbar_init(b_kfull + 8 * i, 1);
@@ -292,9 +297,10 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       for (int t = 0; t < n_tiles && !failed; ++t) {
         const int st = t % C::NKV;
         const uint64_t kb = dk + static_cast<uint64_t>(st * (C::KV_BYTES >> 4));
-        const uint32_t sd = tmem + C::S_COL + (t & 1) * 128;
+        const int sb = t % C::NS;
+        const uint32_t sd = tmem + C::S_COL + sb * 128;
         wait_or_flag(b_kfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
-        if (t >= 2) wait_or_flag(b_sfree + 8 * (t & 1), ((t >> 1) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        if (t >= C::NS) wait_or_flag(b_sfree + 8 * sb, ((t / C::NS) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
         if (failed) break;
         tc_fence_after();
 #pragma unroll
@@ -303,7 +309,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
           mma_f8(sd, dq + off, kb + off, id_qk, ks > 0 ? 1 : 0);
         }
         mma_commit(b_kempty + 8 * st);
-        mma_commit(b_sfull + 8 * (t & 1));
+        mma_commit(b_sfull + 8 * sb);
       }
     }
   } else if (have && warp == 21) {
@@ -384,9 +390,10 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       const int n0 = (s.t_lo + t) * TNK;
       const int c_base = n0 + hf * CW;
       const bool need_mask = (n0 + TNK > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
-      wait_or_flag(b_sfull + 8 * g, u & 1, failed, p.status, GA_ST_WAIT_FULL);
+      const int sb = t % C::NS;            // score buffer of this tile
+      wait_or_flag(b_sfull + 8 * sb, (t / C::NS) & 1, failed, p.status, GA_ST_WAIT_FULL);
       tc_fence_after();
-      const uint32_t s_addr = lane_base + C::S_COL + g * 128 + hf * CW;
+      const uint32_t s_addr = lane_base + C::S_COL + sb * 128 + hf * CW;
       // pass 1: row max of the masked, scaled scores, 32 columns at a time (the scores stay in tensor memory)
       float mx = -INFINITY;
       if (warp_live) {
@@ -458,7 +465,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       }
       // S has been read for the last time: the buffer may take the scores of tile t + 2
       tc_fence_before();
-      mbar_arrive(b_sfree + 8 * g);
+      mbar_arrive(b_sfree + 8 * sb);
       // The residual term of P is only needed while a row rests on few keys: once this thread's share of the row
       // sum stands for at least 32 keys at the running max, the e4m3 rounding of P averages out far below the
       // tolerance. The vote is for this group's next tile (read there after the wait for this tile's PV MMAs,
