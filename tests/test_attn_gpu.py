@@ -24,6 +24,7 @@ GOLD = os.path.join(os.path.dirname(__file__), "golden")
 HD128 = dict(q_heads=8, kv_heads=2, head_dim=128)     # GQA 4
 HD128_G8 = dict(q_heads=16, kv_heads=2, head_dim=128)  # GQA 8
 HD256 = dict(q_heads=4, kv_heads=2, head_dim=256)     # GQA 2
+HD256_G6 = dict(q_heads=12, kv_heads=2, head_dim=256)  # GQA 6: a group size that is not a power of two
 LENS = [1, 2, 127, 128, 129, 255, 1000, 4097]
 
 
@@ -133,6 +134,22 @@ def test_ragged_lengths_hd256(page, qlen):
 def test_gqa8_rows(qlen):
     lens = [max(L, qlen) for L in LENS]
     check(W.make_paged_case(lens, [qlen] * len(lens), 64, seed=50 + qlen, descale="rand", **HD128_G8))
+
+
+@pytest.mark.parametrize("qlen", [1, 2, 3, 5, 16])
+def test_gqa6_hd256_rows(qlen):
+    """head_dim 256 with 6 query heads per kv head, one of the reference's instance shapes
+    (``green_attention/attn_decode.py:58-68``): rows per kv head 6 .. 96, over every row-count instance."""
+    lens = [max(L, qlen) for L in LENS]
+    check(W.make_paged_case(lens, [qlen] * len(lens), 64, seed=80 + qlen, descale="rand", **HD256_G6))
+
+
+def test_gqa6_hd256_extend():
+    """128 rows do not divide by 6: a query block is 21 tokens x 6 heads, two rows of the tile stay empty."""
+    lens = [700, 129, 2048, 33, 21, 22]
+    qlens = [700, 64, 333, 5, 21, 22]
+    check_extend(W.make_paged_case(lens, qlens, 64, seed=86, descale="rand", **HD256_G6))
+    check_extend(W.make_paged_case(lens, qlens, 16, seed=87, window=(1023, 0), **HD256_G6))
 
 
 @pytest.mark.parametrize("page", [1, 16])
