@@ -17,7 +17,7 @@ ABI_VERSION = 1
 
 EXPORTS = (
     "ga_init", "ga_attn_workspace_bytes", "ga_attn_decode", "ga_attn_extend", "ga_attn_decode_noalloc", "ga_attn_merge",
-    "ga_gdn_recurrent", "ga_fp8_tensor_peak", "ga_last_launch_count", "ga_attn_workspace_status", "ga_last_error",
+    "ga_gdn_recurrent", "ga_gdn_verify", "ga_fp8_tensor_peak", "ga_last_launch_count", "ga_attn_workspace_status", "ga_last_error",
     "ga_abi_version", "ga_sm_count",
 )
 
@@ -71,6 +71,26 @@ class GaGdnParams(ctypes.Structure):
     ]
 
 
+class GaGdnVerifyParams(ctypes.Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("a", c_void_p), ("b", c_void_p),
+        ("q_stride_tok", c_int64), ("k_stride_tok", c_int64), ("v_stride_tok", c_int64),
+        ("a_stride_tok", c_int64), ("b_stride_tok", c_int64),
+        ("A_log", c_void_p), ("dt_bias", c_void_p), ("dt_bias_is_bf16", c_int32),
+        ("checkpoint_state", c_void_p), ("state_is_bf16", c_int32), ("state_stride_slot", c_int64),
+        ("d_cache", c_void_p), ("rawv_cache", c_void_p), ("k_cache", c_void_p), ("rawk_cache", c_void_p),
+        ("g_cache", c_void_p),
+        ("d_stride_slot", c_int64), ("rawv_stride_slot", c_int64), ("k_stride_slot", c_int64),
+        ("rawk_stride_slot", c_int64), ("g_stride_slot", c_int64),
+        ("ssm_state_indices", c_void_p), ("state_indices_is_i64", c_int32),
+        ("replay_indices", c_void_p), ("replay_indices_is_i64", c_int32),
+        ("query_start_loc", c_void_p), ("write_pos", c_void_p), ("cache_base", c_void_p), ("is_flush", c_void_p),
+        ("out", c_void_p), ("o_stride_tok", c_int64),
+        ("batch", c_int32), ("h", c_int32), ("hv", c_int32), ("k_dim", c_int32), ("v_dim", c_int32),
+        ("ring_len", c_int32), ("scale", c_float),
+    ]
+
+
 _lock = threading.Lock()
 _lib = None
 
@@ -94,7 +114,8 @@ def lib() -> ctypes.CDLL:
         handle.ga_attn_workspace_bytes.restype = c_size_t
         for name, ptype in (("ga_attn_decode", GaAttnParams), ("ga_attn_extend", GaAttnParams),
                             ("ga_attn_decode_noalloc", GaAttnParams),
-                            ("ga_attn_merge", GaMergeParams), ("ga_gdn_recurrent", GaGdnParams)):
+                            ("ga_attn_merge", GaMergeParams), ("ga_gdn_recurrent", GaGdnParams),
+                            ("ga_gdn_verify", GaGdnVerifyParams)):
             fn = getattr(handle, name)
             fn.argtypes = [POINTER(ptype), c_void_p]
             fn.restype = c_int

@@ -16,6 +16,7 @@
 #include "attn_rows.cuh"
 #include "attn_tc.cuh"
 #include "gdn_recurrent.cuh"
+#include "gdn_verify.cuh"
 
 namespace {
 
@@ -520,6 +521,66 @@ int ga_gdn_recurrent(const GaGdnParams* g, void* stream) {
   else if (g->tokens <= 4) rc = launch_gdn<4>(d, bf, (int)blocks, st);
   else rc = launch_gdn<8>(d, bf, (int)blocks, st);
   if (rc) return rc;
+  g_launches = 1;
+  return 0;
+}
+
+int ga_gdn_verify(const GaGdnVerifyParams* g, void* stream) {
+  int dev;
+  if (current_device(&dev)) return 1;
+  if (!g) return fail("null params");
+  if (g->k_dim != ga::gdn::KD || g->v_dim != ga::gdn::VD) return fail("k_dim/v_dim must be 128");
+  if (g->h <= 0 || g->hv <= 0 || g->hv % g->h) return fail("hv %d must be a multiple of h %d", g->hv, g->h);
+  if (g->ring_len != 16 && g->ring_len != 32) return fail("ring_len %d must be 16 or 32", g->ring_len);
+  if (g->batch <= 0) return fail("batch %d", g->batch);
+  if (!g->q || !g->k || !g->v || !g->a || !g->b || !g->A_log || !g->dt_bias || !g->checkpoint_state || !g->d_cache ||
+      !g->rawv_cache || !g->k_cache || !g->rawk_cache || !g->g_cache || !g->ssm_state_indices || !g->replay_indices ||
+      !g->query_start_loc || !g->write_pos || !g->cache_base || !g->is_flush || !g->out)
+    return fail("null tensor pointer");
+  if (reinterpret_cast<uintptr_t>(g->checkpoint_state) % 16 || g->state_stride_slot % 4)
+    return fail("state must be 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(g->k_cache) % 16 || g->k_stride_slot % 8)
+    return fail("k_cache rows must be 16-byte aligned");
+  ga::gdn::GdnVerifyDev d;
+  std::memset(&d, 0, sizeof(d));
+  d.q = static_cast<const __nv_bfloat16*>(g->q);
+  d.k = static_cast<const __nv_bfloat16*>(g->k);
+  d.v = static_cast<const __nv_bfloat16*>(g->v);
+  d.a = static_cast<const __nv_bfloat16*>(g->a);
+  d.b = static_cast<const __nv_bfloat16*>(g->b);
+  d.q_ts = g->q_stride_tok, d.k_ts = g->k_stride_tok, d.v_ts = g->v_stride_tok;
+  d.a_ts = g->a_stride_tok, d.b_ts = g->b_stride_tok;
+  d.A_log = g->A_log;
+  d.dt_bias = g->dt_bias;
+  d.dt_bias_bf16 = g->dt_bias_is_bf16;
+  d.state = g->checkpoint_state;
+  d.state_bf16 = g->state_is_bf16;
+  d.state_slot = g->state_stride_slot;
+  d.d_cache = static_cast<__nv_bfloat16*>(g->d_cache);
+  d.rawv_cache = static_cast<__nv_bfloat16*>(g->rawv_cache);
+  d.k_cache = static_cast<__nv_bfloat16*>(g->k_cache);
+  d.rawk_cache = static_cast<__nv_bfloat16*>(g->rawk_cache);
+  d.g_cache = g->g_cache;
+  d.d_ss = g->d_stride_slot, d.rawv_ss = g->rawv_stride_slot, d.k_ss = g->k_stride_slot;
+  d.rawk_ss = g->rawk_stride_slot, d.g_ss = g->g_stride_slot;
+  d.sidx = g->ssm_state_indices;
+  d.sidx_i64 = g->state_indices_is_i64;
+  d.ridx = g->replay_indices;
+  d.ridx_i64 = g->replay_indices_is_i64;
+  d.qsl = g->query_start_loc;
+  d.write_pos = g->write_pos;
+  d.cache_base = g->cache_base;
+  d.is_flush = reinterpret_cast<const signed char*>(g->is_flush);
+  d.out = static_cast<__nv_bfloat16*>(g->out);
+  d.o_ts = g->o_stride_tok;
+  d.batch = g->batch, d.h = g->h, d.hv = g->hv, d.L = g->ring_len;
+  d.scale = g->scale;
+  const long long blocks = static_cast<long long>(g->batch) * g->hv;
+  if (blocks > 0x7fffffffLL) return fail("batch * hv too large");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (g->state_is_bf16) ga::gdn::gdn_verify_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), ga::gdn::THREADS, 0, st>>>(d);
+  else ga::gdn::gdn_verify_kernel<float><<<static_cast<unsigned>(blocks), ga::gdn::THREADS, 0, st>>>(d);
+  GA_CUDA(cudaGetLastError());
   g_launches = 1;
   return 0;
 }

@@ -13,6 +13,10 @@ Added for speculative decoding with in-place commit (``gdn_spec_decode`` / op ``
 draft tokens per request, outputs for every token, and the stored state replaced by the state after
 ``accept_lens[n]`` tokens (0 = untouched, bit for bit).
 
+Replay-SSM verify (``gdn_replayssm_verify`` and the AROUND hook on SGLang's ``gdn_replayssm_spec_decode``): up to 4
+chained tokens against a read-only checkpoint state plus the ring of deltas committed since, new deltas into the
+ring, state untouched (``docs/gdn-contract.md:75-132`` of the reference).
+
 Geometry is read from the tensors (``K = V = 128``, any ``HV`` that is a multiple of ``H``) instead of the
 reference's compile-time ``H, HV = 16, 48``.
 """
@@ -246,6 +250,161 @@ def gdn_spec_decode(**kwargs) -> torch.Tensor:
     if not callable(run):
         raise dispatch.Declined(f"gdn_spec_decode: {run}")
     return run(**kwargs)
+
+
+# --------------------------------------------------------------------------- Replay-SSM verify
+
+REPLAY_TARGET = (
+    "sglang.kernels.ops.attention.linear.gdn_replayssm_spec_decode."
+    "gdn_replayssm_spec_decode"
+)
+RING_LENS = (16, 32)
+MAX_REPLAY_SPEC = 4
+
+
+def _verify_supported(call) -> Optional[str]:
+    """Why the Replay-SSM verify kernel cannot serve ``call`` (keyword arguments of
+    ``gdn_replayssm_spec_decode``), or None. Same limits as the reference states for its own kernel
+    (``green_attention/gdn_recurrent.py:269-352``, ``docs/gdn-contract.md:130-132``), with the head counts read
+    from the tensors instead of fixed at 16 / 48."""
+    if call.get("launch_mode") != "verify":
+        return f"launch_mode {call.get('launch_mode')!r}"
+    st = call.get("checkpoint_state")
+    if not isinstance(st, torch.Tensor) or st.ndim != 4:
+        return "no checkpoint_state [slots, HV, V, K]"
+    if st.dtype not in (torch.float32, torch.bfloat16):
+        return f"state dtype {st.dtype}"
+    hv = st.shape[1]
+    q, k, v = call.get("q"), call.get("k"), call.get("v")
+    if not all(isinstance(t, torch.Tensor) for t in (q, k, v, call.get("a"), call.get("b"))):
+        return "missing activation tensor"
+    h = q.shape[1] if q.ndim == 3 else q.shape[-1] // K
+    if tuple(st.shape[2:]) != (V, K) or st.stride(3) != 1 or st.stride(2) != K or st.stride(1) != V * K:
+        return f"state layout {tuple(st.shape)} {st.stride()}"
+    if h <= 0 or hv % h:
+        return f"{hv} value heads over {h} key heads"
+    L = int(call.get("max_cache_len") or 0)
+    for name, shape, dt in (
+        ("d_cache", (hv, L, V), torch.bfloat16), ("rawv_cache", (hv, L, V), torch.bfloat16),
+        ("k_cache", (h, L, K), torch.bfloat16), ("rawk_cache", (h, L, K), torch.bfloat16),
+        ("g_cache", (hv, L), torch.float32),
+    ):
+        t = call.get(name)
+        if not isinstance(t, torch.Tensor):
+            return f"missing {name}"
+        if L not in RING_LENS:
+            return f"max_cache_len {L} not in {RING_LENS}"
+        if t.dtype is not dt:
+            return f"{name} dtype {t.dtype}"
+        if t.ndim != len(shape) + 1 or tuple(t.shape[1:]) != shape:
+            return f"{name} shape {tuple(t.shape)}"
+        if not t[0].is_contiguous() or t.stride(0) % 8:
+            return f"{name} strides {t.stride()}"
+    if call.get("beta_cache") is not None:
+        return "beta_cache unsupported"
+    if int(call.get("max_spec_len") or 0) > MAX_REPLAY_SPEC:
+        return f"max_spec_len {call.get('max_spec_len')}"
+    if call.get("use_qk_l2norm_in_kernel") is not True:
+        return "use_qk_l2norm_in_kernel must be True"
+    if call.get("null_block_id", -1) != -1:
+        return f"null_block_id {call.get('null_block_id')}"
+    why = []
+    for name, t, n, dim in (("q", q, h, K), ("k", k, h, K), ("v", v, hv, V)):
+        if t.dtype is not torch.bfloat16:
+            why.append(f"{name} dtype {t.dtype}")
+        if t.ndim == 3:  # [T, n, dim] with dense heads
+            if tuple(t.shape[1:]) != (n, dim) or t.stride(2) != 1 or t.stride(1) != dim or t.stride(0) % 8:
+                why.append(f"{name} layout {tuple(t.shape)} {t.stride()}")
+        elif t.ndim == 2:  # flattened [T, n * dim]
+            if t.shape[1] != n * dim or t.stride(1) != 1 or t.stride(0) % 8:
+                why.append(f"{name} layout {tuple(t.shape)} {t.stride()}")
+        else:
+            why.append(f"{name} layout {tuple(t.shape)}")
+    T = q.shape[0]
+    for name in ("a", "b"):
+        t = call[name]
+        if t.dtype is not torch.bfloat16 or t.shape[0] != T or t.shape[-1] != hv or t.stride(-1) != 1:
+            why.append(f"{name} {t.dtype} {tuple(t.shape)}")
+    A_log, dt_bias = call.get("A_log"), call.get("dt_bias")
+    if not isinstance(A_log, torch.Tensor) or A_log.dtype is not torch.float32 or A_log.numel() != hv:
+        why.append("A_log must be fp32 [HV]")
+    if not isinstance(dt_bias, torch.Tensor) or dt_bias.dtype not in (torch.float32, torch.bfloat16) or dt_bias.numel() != hv:
+        why.append("dt_bias must be fp32/bf16 [HV]")
+    if why:
+        return "; ".join(why)
+    ri, si, qsl = call.get("replay_indices"), call.get("ssm_state_indices"), call.get("query_start_loc")
+    for name, t in (("ssm_state_indices", si), ("replay_indices", ri)):
+        if not isinstance(t, torch.Tensor) or t.dtype not in (torch.int32, torch.int64) or not t.is_contiguous():
+            return f"{name} must be a contiguous int32/int64 tensor"
+    B = int(ri.numel())
+    if si.numel() != B or not isinstance(qsl, torch.Tensor) or qsl.dtype is not torch.int32 or qsl.numel() != B + 1:
+        return "ssm_state_indices / query_start_loc do not match replay_indices"
+    for name, dt in (("write_pos", torch.int32), ("cache_base", torch.int32), ("is_flush", torch.int8)):
+        t = call.get(name)
+        if not isinstance(t, torch.Tensor) or t.dtype is not dt or not t.is_contiguous():
+            return f"{name} must be a contiguous {dt} tensor"
+    scale = call.get("scale")
+    if scale is not None and abs(float(scale) - K**-0.5) > 1e-9:
+        return f"scale {scale}"
+    out = call.get("out")
+    if not isinstance(out, torch.Tensor) or out.dtype is not torch.bfloat16 or out.shape[0] != T:
+        return "out must be bf16 [T, HV, V]"
+    if out.ndim == 3:
+        if tuple(out.shape[1:]) != (hv, V) or out.stride(2) != 1 or out.stride(1) != V:
+            return f"out layout {tuple(out.shape)} {out.stride()}"
+    elif out.ndim != 2 or out.shape[1] != hv * V or out.stride(1) != 1:
+        return f"out layout {tuple(out.shape)} {out.stride()}"
+    return None
+
+
+def _run_verify(call) -> torch.Tensor:
+    """Launch the Replay-SSM verify kernel on a call that ``_verify_supported`` accepted."""
+    ensure_ready(call["q"].device)
+    q, st, out = call["q"], call["checkpoint_state"], call["out"]
+    p = _C.GaGdnVerifyParams()
+    p.q, p.k, p.v, p.a, p.b = (call[n].data_ptr() for n in ("q", "k", "v", "a", "b"))
+    p.q_stride_tok, p.k_stride_tok, p.v_stride_tok = q.stride(0), call["k"].stride(0), call["v"].stride(0)
+    p.a_stride_tok, p.b_stride_tok = call["a"].stride(0), call["b"].stride(0)
+    p.A_log, p.dt_bias = call["A_log"].data_ptr(), call["dt_bias"].data_ptr()
+    p.dt_bias_is_bf16 = int(call["dt_bias"].dtype is torch.bfloat16)
+    p.checkpoint_state, p.state_is_bf16, p.state_stride_slot = st.data_ptr(), int(st.dtype is torch.bfloat16), st.stride(0)
+    for field, name in (("d", "d_cache"), ("rawv", "rawv_cache"), ("k", "k_cache"), ("rawk", "rawk_cache"), ("g", "g_cache")):
+        setattr(p, name, call[name].data_ptr())
+        setattr(p, f"{field}_stride_slot", call[name].stride(0))
+    si, ri = call["ssm_state_indices"], call["replay_indices"]
+    p.ssm_state_indices, p.state_indices_is_i64 = si.data_ptr(), int(si.dtype is torch.int64)
+    p.replay_indices, p.replay_indices_is_i64 = ri.data_ptr(), int(ri.dtype is torch.int64)
+    p.query_start_loc = call["query_start_loc"].data_ptr()
+    p.write_pos, p.cache_base, p.is_flush = (call[n].data_ptr() for n in ("write_pos", "cache_base", "is_flush"))
+    p.out, p.o_stride_tok = out.data_ptr(), out.stride(0)
+    p.batch = int(ri.numel())
+    p.hv = st.shape[1]
+    p.h = q.shape[1] if q.ndim == 3 else q.shape[-1] // K
+    p.k_dim, p.v_dim, p.ring_len = K, V, int(call["max_cache_len"])
+    p.scale = K**-0.5 if call.get("scale") is None else float(call["scale"])
+    _C.check(_C.lib().ga_gdn_verify(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream), "ga_gdn_verify")
+    return out
+
+
+def gdn_replayssm_verify(**call) -> torch.Tensor:
+    """The Replay-SSM verify step through the C ABI; raises ``dispatch.Declined`` with the reason when the call is
+    outside what the kernel serves."""
+    reason = _verify_supported(call)
+    if reason is not None:
+        raise dispatch.Declined(f"gdn_replayssm_verify: {reason}")
+    return _run_verify(call)
+
+
+def _replayssm_around(original, *args, **kwargs):
+    """AROUND hook on SGLang's ``gdn_replayssm_spec_decode`` (``green_attention/gdn_recurrent.py:355-367``): serve the
+    call when it is a production verify call, hand everything else to the stock function. No allocation and no
+    host synchronisation, so it also runs while the target-verify CUDA graph is captured."""
+    if kwargs and _on_green_sm100() and dispatch.enabled("gdn_verify"):
+        reason = _verify_supported(kwargs)
+        if reason is None:
+            return _run_verify(kwargs)
+        dispatch.log_fallback("gdn_verify", (reason,), kwargs)
+    return original(*args, **kwargs)
 
 
 dispatch.register("gdn_decode", _select_packed, _prewarm)

@@ -68,7 +68,7 @@ def register() -> None:
     from sglang.srt.layers.attention.attention_registry import register_attention_backend
     from sglang.srt.plugins.hook_registry import HookRegistry, HookType
 
-    from greenattention_b200 import gdn
+    from greenattention_b200 import gdn, gdn_recurrent
 
     add_attention_backend_choices([BACKEND])
     add_chunked_prefix_cache_attention_backend(BACKEND)
@@ -76,3 +76,4 @@ def register() -> None:
     add_radix_supported_deterministic_attention_backend_choices([BACKEND])
     register_attention_backend(BACKEND)(_create_green_backend)
     HookRegistry.register(gdn.TARGET, gdn.gdn_init_around, HookType.AROUND)
+    HookRegistry.register(gdn_recurrent.REPLAY_TARGET, gdn_recurrent._replayssm_around, HookType.AROUND)

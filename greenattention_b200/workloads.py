@@ -224,6 +224,84 @@ def make_gdn_case(
     )
 
 
+def make_gdn_replay_case(
+    spec_lens, *, h=16, hv=32, ring_len=32, write_pos=None, cache_base=None, pad_rows=(), flush_rows=(), seed=6,
+    device="cpu", state_dtype=torch.float32, state_std=0.02, flat=False, idx_dtype=torch.int32,
+):
+    """Keyword arguments of one Replay-SSM verify call (``gdn_replayssm_spec_decode``, ``launch_mode="verify"``;
+    layouts of ``docs/gdn-contract.md:83-95`` in the reference): ``spec_lens[n]`` in 0..4 draft tokens per request,
+    ring slot n for request n with ``write_pos[n]`` committed entries starting at physical position
+    ``cache_base[n]`` (random when None), history deltas N(0, 0.05), history keys L2-normalised, history gates in
+    (-1, 0). ``flat``: q/k/v/out given as ``[T, heads * dim]``."""
+    dev = torch.device(device)
+    g = _gen(seed, dev)
+    B, T, L = len(spec_lens), int(sum(spec_lens)), ring_len
+    k, v = 128, 128
+    ring = B
+    qsl = torch.tensor([0] + list(torch.tensor(list(spec_lens)).cumsum(0).tolist()), dtype=torch.int32, device=dev)
+
+    def unit(*shape):
+        x = torch.randn(shape, generator=g, device=dev)
+        return x / x.norm(dim=-1, keepdim=True)
+
+    wp = torch.randint(0, L + 1, (ring + 1,), generator=g, device=dev) if write_pos is None else \
+        torch.tensor(list(write_pos) + [0], device=dev)
+    cb = torch.randint(0, L, (ring + 1,), generator=g, device=dev) if cache_base is None else \
+        torch.tensor(list(cache_base) + [0], device=dev)
+    slots = B + 4
+    sidx = torch.randperm(slots, generator=g, device=dev)[:B]
+    for r in pad_rows:
+        sidx[r] = -1
+    fl = torch.zeros(ring + 1, dtype=torch.int8, device=dev)
+    for r in flush_rows:
+        fl[r] = 1
+    q, kk = unit(max(T, 1), h, k)[:T], unit(max(T, 1), h, k)[:T]
+    vv = torch.randn((T, hv, v), generator=g, device=dev)
+    call = dict(
+        q=q.to(torch.bfloat16), k=kk.to(torch.bfloat16), v=vv.to(torch.bfloat16),
+        a=torch.randn((T, hv), generator=g, device=dev).to(torch.bfloat16),
+        b=torch.randn((T, hv), generator=g, device=dev).to(torch.bfloat16),
+        A_log=torch.log(torch.rand(hv, generator=g, device=dev) * 2 + 0.1),
+        dt_bias=torch.randn(hv, generator=g, device=dev) * 0.5,
+        checkpoint_state=(torch.randn((slots, hv, v, k), generator=g, device=dev) * state_std).to(state_dtype),
+        d_cache=(torch.randn((ring, hv, L, v), generator=g, device=dev) * 0.05).to(torch.bfloat16),
+        rawv_cache=torch.zeros((ring, hv, L, v), dtype=torch.bfloat16, device=dev),
+        k_cache=unit(ring, h, L, k).to(torch.bfloat16),
+        rawk_cache=torch.zeros((ring, h, L, k), dtype=torch.bfloat16, device=dev),
+        g_cache=-torch.rand((ring, hv, L), generator=g, device=dev),
+        beta_cache=None,
+        out=torch.full((T, hv, v), 7.0, dtype=torch.bfloat16, device=dev),
+        query_start_loc=qsl, ssm_state_indices=sidx.to(idx_dtype),
+        replay_indices=torch.arange(B, device=dev).to(idx_dtype),
+        write_pos=wp.to(torch.int32), cache_base=cb.to(torch.int32), is_flush=fl,
+        launch_mode="verify", null_block_id=-1, scale=k**-0.5, use_qk_l2norm_in_kernel=True,
+        max_spec_len=4, max_cache_len=L,
+    )
+    if flat:
+        for name in ("q", "k", "v", "out"):
+            call[name] = call[name].reshape(T, -1)
+    return call
+
+
+def gdn_replay_bytes(call: dict) -> int:
+    """Algorithmic bytes of one Replay-SSM verify call: the checkpoint tile of every live (request, value head)
+    read once, plus the history rows read and the ring rows / outputs written."""
+    st = call["checkpoint_state"]
+    hv, L = st.shape[1], call["d_cache"].shape[2]
+    h = call["k_cache"].shape[1]
+    qsl = call["query_start_loc"].tolist()
+    total = 0
+    for n, (si, ri) in enumerate(zip(call["ssm_state_indices"].tolist(), call["replay_indices"].tolist())):
+        nt = min(qsl[n + 1] - qsl[n], 4)
+        if nt <= 0 or si < 0 or int(call["is_flush"][ri]) != 0:
+            continue
+        W = min(max(int(call["write_pos"][ri]), 0), L)
+        total += hv * 128 * 128 * st.element_size()
+        total += W * (hv * (128 * 2 + 4) + h * 128 * 2)
+        total += nt * (hv * 128 * 2 * 3 + h * 128 * 2 * 2)
+    return total
+
+
 def c5_gdn_spec(device="cuda", seed=5, batch=256, tokens=4):
     """Batch 256, 16 qk / 32 v heads, d_k = d_v = 128, fp32 state N(0, 0.02), 4 draft tokens,
     accepted-prefix lengths uniform in 0..4."""

@@ -17,6 +17,8 @@
  *   ga_gdn_recurrent   <- `gdn_decode` export,       csrc/sm90/gdn_recurrent/launcher.cu:69-112
  *                         (and the chained-token part of `gdn_verify`, launcher.cu:117-177)
  *   GaGdnParams        <- `DecodeParams`,            csrc/sm90/gdn_recurrent/kernel.cuh:155-173
+ *   ga_gdn_verify      <- `gdn_verify` export,       csrc/sm90/gdn_recurrent/launcher.cu:117-177
+ *   GaGdnVerifyParams  <- `VerifyParams`,            csrc/sm90/gdn_recurrent/verify.cuh:67-100
  *   the loader itself  <- green_attention/jit.py:139-183 (runtime nvcc build + tvm_ffi module)
  */
 #ifndef GREEN_ATTENTION_H_
@@ -107,6 +109,46 @@ typedef struct GaGdnParams {
   float scale;
 } GaGdnParams;
 
+/* Replay-SSM speculative verify (docs/gdn-contract.md:75-132 of the reference): up to 4 chained tokens per
+ * request against a read-only checkpoint state plus the ring of deltas committed since that checkpoint. Writes
+ * `out` and, while the ring has room (write_pos + j < ring_len), the new delta / key / gate rows of the ring;
+ * never the state, write_pos, cache_base or is_flush. A request whose state slot is < 0 gets zero output rows
+ * and nothing else; one whose ring slot has is_flush != 0 is skipped entirely. */
+typedef struct GaGdnVerifyParams {
+  const void* q;  /* bf16 [T, H, K]: token t, head h at q + t*q_stride_tok + h*k_dim (T = sum of spec lens) */
+  const void* k;
+  const void* v;  /* bf16 [T, HV, V] */
+  const void* a;  /* bf16 [T, HV] */
+  const void* b;
+  int64_t q_stride_tok, k_stride_tok, v_stride_tok, a_stride_tok, b_stride_tok; /* elements */
+  const float* A_log;    /* [HV] fp32 */
+  const void* dt_bias;   /* [HV] fp32 or bf16 */
+  int32_t dt_bias_is_bf16;
+  const void* checkpoint_state; /* [slots, HV, V, K], K contiguous, fp32 or bf16; read only */
+  int32_t state_is_bf16;
+  int64_t state_stride_slot;
+  void* d_cache;         /* bf16 [ring, HV, L, V]: high part of the committed deltas (read: history; written: new) */
+  void* rawv_cache;      /* bf16 [ring, HV, L, V]: residual of the new deltas (written only) */
+  void* k_cache;         /* bf16 [ring, H, L, K]: high part of the normalised keys */
+  void* rawk_cache;      /* bf16 [ring, H, L, K]: residual of the new keys (written only) */
+  float* g_cache;        /* fp32 [ring, HV, L] */
+  int64_t d_stride_slot, rawv_stride_slot, k_stride_slot, rawk_stride_slot, g_stride_slot; /* elements; dense within a slot */
+  const void* ssm_state_indices; /* [batch] int32 or int64 checkpoint slot; < 0 = PAD */
+  int32_t state_indices_is_i64;
+  const void* replay_indices;    /* [batch] int32 or int64 ring slot */
+  int32_t replay_indices_is_i64;
+  const int32_t* query_start_loc; /* [batch + 1]; spec len of request n = qsl[n+1] - qsl[n] in 0..4 */
+  const int32_t* write_pos;       /* [ring + 1] entries already in the ring of a slot */
+  const int32_t* cache_base;      /* [ring + 1] physical position of entry 0 */
+  const int8_t* is_flush;         /* [ring + 1] */
+  void* out;             /* bf16 [T, HV, V]: token t at out + t*o_stride_tok */
+  int64_t o_stride_tok;
+  int32_t batch;
+  int32_t h, hv, k_dim, v_dim;   /* k_dim == v_dim == 128; hv % h == 0 */
+  int32_t ring_len;              /* L: 16 or 32 */
+  float scale;
+} GaGdnVerifyParams;
+
 /* Once per process and device, before the first launch and before any graph capture: resolves the
  * driver entry point used to encode TMA descriptors and raises the dynamic shared memory limit of every
  * kernel instance. Idempotent. */
@@ -138,6 +180,7 @@ int ga_attn_extend(const GaAttnParams* p, void* stream);
 int ga_attn_decode_noalloc(const GaAttnParams* p, void* stream);
 int ga_attn_merge(const GaMergeParams* p, void* stream);
 int ga_gdn_recurrent(const GaGdnParams* p, void* stream);
+int ga_gdn_verify(const GaGdnVerifyParams* p, void* stream);
 
 /* Number of kernels the last successful call on this thread launched (bench bookkeeping). */
 int ga_last_launch_count(void);

@@ -224,7 +224,7 @@ def test_struct_layouts_match_the_header():
     with open(os.path.join(ROOT, "include", "green_attention.h")) as f:
         header = f.read()
     for cname, ctype in (("GaAttnParams", _C.GaAttnParams), ("GaMergeParams", _C.GaMergeParams),
-                         ("GaGdnParams", _C.GaGdnParams)):
+                         ("GaGdnParams", _C.GaGdnParams), ("GaGdnVerifyParams", _C.GaGdnVerifyParams)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), header, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         names = []
