@@ -173,12 +173,33 @@ def bench_gdn(dev, steps, warmup, hbm_gbs):
     ms = sorted(s.elapsed_time(e) for s, e in ev)
     med = ms[len(ms) // 2]
     tokens = c["q"].shape[0] * c["q"].shape[1]
-    return {
+    res = {
         "workload": "C5 GDN spec: B=256, H16/HV32, K=V=128, fp32 state, 4 draft tokens, accept~U{0..4}",
         "us_per_call": med * 1e3, "verified_tok_per_s": tokens / (med * 1e-3), "algorithmic_bytes": nbytes,
         "hbm_gbs": nbytes / (med * 1e-3) / 1e9, "hbm_frac": nbytes / (med * 1e-3) / 1e9 / hbm_gbs,
         "l2": "flushed by a 512 MB write before each call",
     }
+    del c, kw, start, out
+    # Replay-SSM verify of the same shape: read-only checkpoint, ring of 32 with a random number of entries
+    rc = W.make_gdn_replay_case([4] * 256, h=16, hv=32, ring_len=32, seed=7, device=dev)
+    rbytes = W.gdn_replay_bytes({k: (v.cpu() if isinstance(v, torch.Tensor) and v.numel() < 4096 else v) for k, v in rc.items()})
+    for _ in range(warmup):
+        gdn_recurrent.gdn_replayssm_verify(**rc)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for s, e in ev:
+        flush.zero_()
+        s.record()
+        gdn_recurrent.gdn_replayssm_verify(**rc)
+        e.record()
+    torch.cuda.synchronize()
+    ms = sorted(s.elapsed_time(e) for s, e in ev)
+    med = ms[len(ms) // 2]
+    res["replay_verify"] = {
+        "workload": "Replay-SSM verify: B=256, H16/HV32, fp32 checkpoint (read only), ring 32 with U{0..32} entries, 4 tokens",
+        "us_per_call": med * 1e3, "verified_tok_per_s": 1024 / (med * 1e-3), "algorithmic_bytes": rbytes,
+        "hbm_gbs": rbytes / (med * 1e-3) / 1e9, "hbm_frac": rbytes / (med * 1e-3) / 1e9 / hbm_gbs,
+    }
+    return res
 
 
 def bench_attn_extra(dev, hbm_gbs, steps=5):

@@ -68,7 +68,7 @@ struct VerifyShared {
   float kn[VT][KD];
   float vv[VT][VD];
   float du[VT][VD];            // the new deltas u_j, for the ring write
-  float dh[MAX_RING][VD];      // history deltas (bf16 high part)
+  __align__(16) __nv_bfloat16 dh[MAX_RING][VD];  // history deltas (bf16 high part), filled by cp.async
   float w[MAX_RING][2 * VT];   // decay_c * (khist_c . x'_m), m = k'_0..3, q'_0..3
   float red[4][32];
   float tot[32];
@@ -80,7 +80,7 @@ struct VerifyShared {
 };
 
 template <typename ST>
-__global__ void __launch_bounds__(THREADS, 3) gdn_verify_kernel(const GdnVerifyDev p) {
+__global__ void __launch_bounds__(THREADS, 4) gdn_verify_kernel(const GdnVerifyDev p) {
   constexpr int T = VT;
   __shared__ VerifyShared sh;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -118,6 +118,7 @@ __global__ void __launch_bounds__(THREADS, 3) gdn_verify_kernel(const GdnVerifyD
   // ---------------------------------------------------------------- prologue (whole CTA)
   {
     float qd[T], kd[T];
+    uint4 kraw[4] = {};
 #pragma unroll
     for (int t = 0; t < T; ++t) {
       const bool on = t < nt;
@@ -125,10 +126,21 @@ __global__ void __launch_bounds__(THREADS, 3) gdn_verify_kernel(const GdnVerifyD
       kd[t] = on ? __bfloat162float(p.k[(bos + t) * p.k_ts + h * KD + tid]) : 0.f;
       sh.vv[t][tid] = on ? __bfloat162float(p.v[(bos + t) * p.v_ts + hv * VD + tid]) : 0.f;
     }
-    // history: deltas of this value head (one coalesced 256-byte row per entry) and gates
-    for (int c = 0; c < W; ++c)
-      sh.dh[c][tid] = __bfloat162float(p.d_cache[r * p.d_ss + (static_cast<long long>(hv) * L + ((base + c) & Lm)) * VD + tid]);
+    // History, all requested now so that the latency hides under the reductions below: the deltas of this value
+    // head straight into shared memory (16 threads x 16 bytes per 256-byte ring row), the gates, and this
+    // thread's share of the history keys (four threads per ring entry, 32 of the 128 dims each) into registers.
+    for (int i = tid; i < W * 16; i += THREADS) {
+      const int c = i >> 4, ch = i & 15;
+      cp_async_16(smem_u32(&sh.dh[c][ch * 8]),
+                  p.d_cache + r * p.d_ss + (static_cast<long long>(hv) * L + ((base + c) & Lm)) * VD + ch * 8);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
     if (tid < MAX_RING) sh.gh[tid] = tid < W ? p.g_cache[r * p.g_ss + static_cast<long long>(hv) * L + ((base + tid) & Lm)] : 0.f;
+    if ((tid >> 2) < W) {
+      const __nv_bfloat16* ksrc = p.k_cache + r * p.k_ss + (static_cast<long long>(h) * L + ((base + (tid >> 2)) & Lm)) * KD;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) kraw[i] = *reinterpret_cast<const uint4*>(ksrc + ((tid & 3) + 4 * i) * 8);
+    }
     // one fused block reduction: |q|^2, |k|^2, k_i.k_j (i < j), k_i.q_j (i <= j)
     float pv[32];
 #pragma unroll
@@ -209,12 +221,10 @@ __global__ void __launch_bounds__(THREADS, 3) gdn_verify_kernel(const GdnVerifyD
 #pragma unroll
       for (int m = 0; m < 2 * T; ++m) sc[m] = 0.f;
       if (c < W) {
-        const __nv_bfloat16* ksrc = p.k_cache + r * p.k_ss + (static_cast<long long>(h) * L + ((base + c) & Lm)) * KD;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int d0 = (sub + 4 * i) * 8;
-          const uint4 raw = *reinterpret_cast<const uint4*>(ksrc + d0);
-          const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+          const uint32_t wds[4] = {kraw[i].x, kraw[i].y, kraw[i].z, kraw[i].w};
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const float kx = bf16_bits_to_f32((wds[e >> 1] >> ((e & 1) * 16)) & 0xffffu);
@@ -236,6 +246,7 @@ __global__ void __launch_bounds__(THREADS, 3) gdn_verify_kernel(const GdnVerifyD
 #pragma unroll
         for (int m = 0; m < 2 * T; ++m) sh.w[c][m] = dec * sc[m];
       }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
       __syncthreads();
     }
   }
@@ -271,7 +282,7 @@ __global__ void __launch_bounds__(THREADS, 3) gdn_verify_kernel(const GdnVerifyD
 #pragma unroll
     for (int j = 0; j < T; ++j) dots[j] *= total;
     for (int c = 0; c < W; ++c) {
-      const float dv = sh.dh[c][my_row];
+      const float dv = __bfloat162float(sh.dh[c][my_row]);
 #pragma unroll
       for (int j = 0; j < T; ++j) dots[j] += dv * sh.w[c][mofs + j];
     }
