@@ -578,8 +578,21 @@ int ga_gdn_verify(const GaGdnVerifyParams* g, void* stream) {
   const long long blocks = static_cast<long long>(g->batch) * g->hv;
   if (blocks > 0x7fffffffLL) return fail("batch * hv too large");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (g->state_is_bf16) ga::gdn::gdn_verify_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), ga::gdn::THREADS, 0, st>>>(d);
-  else ga::gdn::gdn_verify_kernel<float><<<static_cast<unsigned>(blocks), ga::gdn::THREADS, 0, st>>>(d);
+  // One CTA per (request, key head) when the value heads of a key head fit its shared memory (2 or 3 per key
+  // head in the served models), else one per (request, value head).
+  const int gsz = g->hv / g->h;
+  const unsigned gblocks = static_cast<unsigned>(static_cast<long long>(g->batch) * g->h);
+  const bool bf = g->state_is_bf16 != 0;
+  if (gsz == 2) {
+    if (bf) ga::gdn::gdn_verify_group_kernel<__nv_bfloat16, 2><<<gblocks, ga::gdn::THREADS, 0, st>>>(d);
+    else ga::gdn::gdn_verify_group_kernel<float, 2><<<gblocks, ga::gdn::THREADS, 0, st>>>(d);
+  } else if (gsz == 3) {
+    if (bf) ga::gdn::gdn_verify_group_kernel<__nv_bfloat16, 3><<<gblocks, ga::gdn::THREADS, 0, st>>>(d);
+    else ga::gdn::gdn_verify_group_kernel<float, 3><<<gblocks, ga::gdn::THREADS, 0, st>>>(d);
+  } else {
+    if (bf) ga::gdn::gdn_verify_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), ga::gdn::THREADS, 0, st>>>(d);
+    else ga::gdn::gdn_verify_kernel<float><<<static_cast<unsigned>(blocks), ga::gdn::THREADS, 0, st>>>(d);
+  }
   GA_CUDA(cudaGetLastError());
   g_launches = 1;
   return 0;
