@@ -115,6 +115,12 @@ const AttnInstance* decode_instance(int hd, int rows) {
   static const AttnInstance t256[5] = {make_instance<256, 1, 4, 2, 0, true>(), make_instance<256, 1, 4, 2, 0>(),
                                        make_instance<256, 2, 2, 2, 0>(), make_instance<256, 4, 1, 2, 0>(),
                                        make_instance<256, 8, 1, 2, 0>()};
+  // 17..24 rows at head_dim 128 (e.g. 5 draft tokens x 4 heads per kv head) when the batch is too small for the
+  // tcgen05 route: three warps with 8 rows each share every tile (transposed-PV path), two such sets alternate
+  // over the tiles. Measured 529 us on the B=64 verify configuration against 590 us for the 32-row instance
+  // (and 340 us for the tcgen05 kernel, which is why large batches go there).
+  static const AttnInstance r24 = make_instance<128, 3, 2, 2, 0, true>();
+  if (hd == 128 && rows > 16 && rows <= 24) return &r24;
   int i = rows <= 8 ? 0 : rows <= 16 ? 1 : rows <= 32 ? 2 : rows <= 64 ? 3 : 4;
   return hd == 128 ? &t128[i] : &t256[i];
 }
@@ -307,7 +313,7 @@ int ga_init(int device) {
     g_encode = reinterpret_cast<EncodeTiledFn>(fn);
   }
   for (int hd : {128, 256}) {
-    for (int rows : {8, 16, 32, 64, 128})
+    for (int rows : {8, 16, 24, 32, 64, 128})
       if (set_smem(*decode_instance(hd, rows))) return 1;
     if (set_smem(*extend_instance(hd)) || set_smem(*extend_tc_instance(hd))) return 1;
   }

@@ -640,9 +640,10 @@ struct RowAcc8 {
 
 template <class C>
 __device__ __forceinline__ void load_q_frags8(const AttnDev& p, const Seg& s, int lane,
-                                              uint32_t (&qf)[C::ATOMS * 4][2], int& pos) {
+                                              uint32_t (&qf)[C::ATOMS * 4][2], int& pos, int row0) {
   const int g = lane >> 2, t = lane & 3;
-  const int tq = g / p.gqa, hq = g - tq * p.gqa;
+  const int row = row0 + g;  // row0: first row of this warp's group of 8
+  const int tq = row / p.gqa, hq = row - tq * p.gqa;
   const bool valid = tq < s.nq;
   pos = valid ? s.pos0 + tq : -1;
   const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1;
@@ -916,7 +917,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
         s = one;
         one_pending = false;
       }
-      load_q_frags8<C>(p, s, lane, qf, pos);
+      load_q_frags8<C>(p, s, lane, qf, pos, 8 * mt);
       acc.reset();
       const float kds = p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f;
       const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
@@ -939,7 +940,8 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
       acc.l += __shfl_xor_sync(0xffffffffu, acc.l, 1);
       acc.l += __shfl_xor_sync(0xffffffffu, acc.l, 2);
       const int valid_rows = s.nq * p.gqa;
-      // this lane's two output columns are query rows 2t and 2t+1; their statistics live in quads 2t, 2t+1
+      // this lane's two output columns are rows 2t and 2t+1 of the warp's group of 8 (group mt when several warps
+      // share the tiles, each with its own 8 rows); their statistics live in quads 2t, 2t+1
       float m_r[2], l_r[2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
@@ -949,7 +951,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
       if (WN == 1) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int r = 2 * t + e;
+          const int r = 8 * mt + 2 * t + e;
           if (r < valid_rows) {
             const float inv = l_r[e] > 0.f ? 1.f / l_r[e] : 0.f;
 #pragma unroll
@@ -963,7 +965,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
           if (wn == round) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              const int r = 2 * t + e;
+              const int r = 8 * mt + 2 * t + e;
               float f_old = 0.f, f_own = 1.f, m_new = m_r[e], l_new = l_r[e];
               if (round > 0) {
                 const float m_old = mergeM[r], l_old = mergeL[r];
