@@ -149,15 +149,22 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-template <int HD>
+template <int HD, bool REP>
 AttnInstance make_tc_instance() {
-  return {ga::attn::tc::attn_tc_kernel<HD>, ga::attn::tc::TC_THREADS, ga::attn::tc::TcCfg<HD>::SMEM_BYTES, 128, 1};
+  return {ga::attn::tc::attn_tc_kernel<HD, REP>, ga::attn::tc::TC_THREADS, ga::attn::tc::TcCfg<HD>::SMEM_BYTES, 128, 1};
 }
 // tcgen05 extend kernel: 128 query rows per CTA, two softmax groups alternating over the key tiles.
 const AttnInstance* extend_tc_instance(int hd) {
-  static const AttnInstance e128 = make_tc_instance<128>();
-  static const AttnInstance e256 = make_tc_instance<256>();
+  static const AttnInstance e128 = make_tc_instance<128, false>();
+  static const AttnInstance e256 = make_tc_instance<256, false>();
   return hd == 128 ? &e128 : &e256;
+}
+// The same kernel for speculative verify with at most 32 rows per kv head: the rows are replicated over the four
+// lane quarters of the query tile so that all four schedulers share the softmax.
+const AttnInstance* verify_tc_instance(int hd) {
+  static const AttnInstance v128 = make_tc_instance<128, true>();
+  static const AttnInstance v256 = make_tc_instance<256, true>();
+  return hd == 128 ? &v128 : &v256;
 }
 
 // The tcgen05 kernel wants TMA-sized pages and 16-byte aligned q / out rows.
@@ -315,7 +322,7 @@ int ga_init(int device) {
   for (int hd : {128, 256}) {
     for (int rows : {8, 16, 24, 32, 64, 128})
       if (set_smem(*decode_instance(hd, rows))) return 1;
-    if (set_smem(*extend_instance(hd)) || set_smem(*extend_tc_instance(hd))) return 1;
+    if (set_smem(*extend_instance(hd)) || set_smem(*extend_tc_instance(hd)) || set_smem(*verify_tc_instance(hd))) return 1;
   }
   GA_CUDA(cudaSetDevice(prev));
   std::lock_guard<std::mutex> lock(g_mu);
@@ -361,7 +368,7 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
   if (rows > 16 && !a->out_is_f32 && tc_aligned(a, d) && a->batch * a->kv_heads >= sm) {
     d.bq = ga::attn::MAX_ROWS / d.gqa;
     d.max_q = 1 << 30;
-    const AttnInstance* tk = extend_tc_instance(a->head_dim);
+    const AttnInstance* tk = rows <= 32 ? verify_tc_instance(a->head_dim) : extend_tc_instance(a->head_dim);
     dim3 tgrid(static_cast<unsigned>(a->total_q / d.bq + a->batch), a->kv_heads);
     tk->fn<<<tgrid, tk->threads, tk->smem, st>>>(d, kmap, vmap);
     GA_CUDA(cudaGetLastError());

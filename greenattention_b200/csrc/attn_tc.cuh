@@ -88,6 +88,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -138,15 +146,15 @@ __device__ __forceinline__ void wait_or_flag(uint32_t bar, uint32_t parity, bool
   }
 }
 
-// exp2 pass over 32 scores of one row held in registers: P = 2^(v * sl2 + sh) as e4m3 (plus the residual term when
+// exp2 pass over N = 32 (or 16) scores of one row held in registers: P = 2^(v * sl2 + sh) as e4m3 (plus the residual term when
 // LO) into two 16-byte chunks of the swizzled P row(s); returns the sum of the unrounded P. MASK and LO are template
 // parameters so that the common tile (below the diagonal, long row) runs the bare FFMA / EX2 / FADD / CVT sequence.
-template <bool MASK, bool LO>
-__device__ __forceinline__ float exp_chunk32(const uint32_t (&v)[32], float sl2, float sh, int col0, int pos, int lo_key,
+template <bool MASK, bool LO, int N = 32>
+__device__ __forceinline__ float exp_chunk32(const uint32_t (&v)[N], float sl2, float sh, int col0, int pos, int lo_key,
                                              uint32_t p_hi, uint32_t p_lo, uint32_t chunk0, uint32_t rx) {
   float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-  for (int c16 = 0; c16 < 2; ++c16) {  // 16 keys = one 16-byte chunk of the P row
+  for (int c16 = 0; c16 < N / 16; ++c16) {  // 16 keys = one 16-byte chunk of the P row
     uint32_t hi[4], lo[4];
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) {
@@ -187,7 +195,9 @@ constexpr int TC_SOFTMAX = 512;
 constexpr int TC_GROUP = 256;
 constexpr int TC_THREADS = TC_SOFTMAX + 192;
 
-template <int HD>
+// REP: instance for calls with at most 32 rows per kv head (see the softmax section); extend uses REP = false so
+// that its inner loops carry none of that mode's branches.
+template <int HD, bool REP>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
                const __grid_constant__ CUtensorMap vmap) {
@@ -347,11 +357,22 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     // dims. While one group is in its exp2 pass (the SM's 16 exp2 per clock are the floor of a tile), the other
     // waits for scores, reads them and finds its row maxima. The running max is one chain over all tiles: a group
     // takes the value the other group published for the tile before, decides, and publishes its own.
+    //
+    // Few rows (speculative verify: query tokens x GQA <= 32): the rows are replicated into all four 32-lane
+    // quarters of the Q tile, so S comes out four times and each quarter's warps take a quarter of the key
+    // columns of the same rows (16 per thread instead of 64). A warp can only read its own quarter of tensor
+    // memory, and a quarter maps to one scheduler: without this the whole softmax of such a call would sit on
+    // one scheduler's exp2 unit. P rows 32..127 are zeroed once; O rows 0..31 are the result.
     const int g = tid >> 8, hf = (tid >> 7) & 1, r = tid & 127;
     const int part = g * 2 + hf;  // quarter of the head dims this thread loads of Q and stores of O
-    const int tq = r / p.gqa, hq = r - tq * p.gqa;
+    const bool rep = REP && s.nq * p.gqa <= 32;
+    const int qt = warp & 3;             // lane quarter of this warp
+    const int rr = rep ? (r & 31) : r;   // the query row this thread works for
+    const int tq = rr / p.gqa, hq = rr - tq * p.gqa;
     const bool valid = tq < s.nq;
-    const bool warp_live = (warp & 3) * 32 < s.nq * p.gqa;  // some row of this warp is a real query row
+    const bool warp_live = rep || qt * 32 < s.nq * p.gqa;  // some row of this warp is a real query row
+    const bool owns_o = !rep || qt == 0;                   // this warp's lanes of O are result rows
+    const int col_first = rep ? 32 * qt + 16 * hf : hf * CW;  // first key column of this thread's share of a tile
     const int pos = valid ? s.pos0 + tq : -1;
     const int lo_key = p.window_left >= 0 ? pos - p.window_left : -(1 << 30);
     {  // Q: a quarter of this row, rounded to e4m3, into the swizzled A tile
@@ -376,8 +397,13 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
                      : "memory");
       }
+      if (rep) {  // P rows 32..127 are never written in this mode and must read as zero
+        for (int i = tid; i < 4 * C::P_BYTES / 16; i += TC_SOFTMAX)
+          asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(sP + i * 16), "r"(0) : "memory");
+      }
       fence_proxy_async();
       mbar_arrive(b_q);
+      if (rep) named_bar_sync(1, TC_SOFTMAX);  // every zero is in place before any thread writes a P row
     }
     const float kds = p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f;
     const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
@@ -388,18 +414,29 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     for (int t = g; t < n_tiles; t += 2) {
       const int u = t >> 1;                // this group's iteration: phases of its own barriers
       const int n0 = (s.t_lo + t) * TNK;
-      const int c_base = n0 + hf * CW;
+      const int c_base = n0 + col_first;
       const bool need_mask = (n0 + TNK > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
       const int sb = t % C::NS;            // score buffer of this tile
       wait_or_flag(b_sfull + 8 * sb, (t / C::NS) & 1, failed, p.status, GA_ST_WAIT_FULL);
       tc_fence_after();
-      const uint32_t s_addr = lane_base + C::S_COL + sb * 128 + hf * CW;
+      const uint32_t s_addr = lane_base + C::S_COL + sb * 128 + col_first;
       // pass 1: row max of the masked, scaled scores, 32 columns at a time (the scores stay in tensor memory)
       float mx = -INFINITY;
       if (warp_live) {
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (rep) {
+          uint32_t v[16];
+          tmem_ld16(s_addr, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int col = c_base + j;
+            const float x = (!need_mask || (col <= pos && col >= lo_key)) ? __uint_as_float(v[j]) : -INFINITY;
+            m4[j & 3] = fmaxf(m4[j & 3], x);
+          }
+        }
 #pragma unroll 1
-        for (int c0 = 0; c0 < CW; c0 += 32) {
+        for (int c0 = 0; c0 < (rep ? 0 : CW); c0 += 32) {
           uint32_t v[32];
           tmem_ld32(s_addr + c0, v);
           tmem_wait_ld();
@@ -421,7 +458,15 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       // only makes P a little smaller)
       mxbuf[(g * 2 + hf) * 128 + r] = __float2bfloat16_ru(mx);
       named_bar_sync(grp_bar, TC_GROUP);
-      mx = fmaxf(__bfloat162float(mxbuf[(g * 2) * 128 + r]), __bfloat162float(mxbuf[(g * 2 + 1) * 128 + r]));
+      if (rep) {  // eight shares of a row: two parts in each of the four quarters
+        mx = -INFINITY;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          mx = fmaxf(mx, fmaxf(__bfloat162float(mxbuf[(g * 2) * 128 + rr + 32 * q4]),
+                               __bfloat162float(mxbuf[(g * 2 + 1) * 128 + rr + 32 * q4])));
+      } else {
+        mx = fmaxf(__bfloat162float(mxbuf[(g * 2) * 128 + r]), __bfloat162float(mxbuf[(g * 2 + 1) * 128 + r]));
+      }
       // the running max after tile t - 1, from the other group
       float m_prev = -INFINITY;
       if (t >= 1) {
@@ -445,10 +490,23 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       const bool with_lo = lo_flag[g * 2 + (u & 1)] != 0u;
       // pass 2: P = 2^(s - m + 7), e4m3 (plus the residual term while needed), into the swizzled A tiles
       if (warp_live) {
-        const uint32_t p_hi = sP + (g * 2) * C::P_BYTES + r * 128, p_lo = p_hi + C::P_BYTES;
+        const uint32_t p_hi = sP + (g * 2) * C::P_BYTES + rr * 128, p_lo = p_hi + C::P_BYTES;
         float lsum = 0.f;
+        if (rep) {
+          uint32_t v[16];
+          tmem_ld16(s_addr, v);
+          tmem_wait_ld();
+          const uint32_t chunk0 = static_cast<uint32_t>(col_first >> 4), rx = static_cast<uint32_t>(rr & 7);
+          if (with_lo) {
+            lsum += need_mask ? exp_chunk32<true, true, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx)
+                              : exp_chunk32<false, true, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx);
+          } else {
+            lsum += need_mask ? exp_chunk32<true, false, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx)
+                              : exp_chunk32<false, false, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx);
+          }
+        }
 #pragma unroll 1
-        for (int c0 = 0; c0 < CW; c0 += 32) {
+        for (int c0 = 0; c0 < (rep ? 0 : CW); c0 += 32) {
           uint32_t v[32];
           tmem_ld32(s_addr + c0, v);
           tmem_wait_ld();
@@ -472,7 +530,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       // which follow every thread's arrival below).
       if (valid && l < 32.f * 128.f) atomicOr(lo_flag + g * 2 + ((u + 1) & 1), 1u);
       // O in tensor memory is rescaled only when some row of this warp moved its max; needs PV of tile t-1 done.
-      if (t >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
+      if (t >= 1 && owns_o && __any_sync(0xffffffffu, alpha != 1.f)) {
         wait_or_flag(b_pfree + 8 * (g ^ 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
         tc_fence_after();
 #pragma unroll 1
@@ -510,7 +568,14 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     named_bar_sync(1, TC_SOFTMAX);  // the row sums overlay the max buffers
     lbuf[part * 128 + r] = l;
     named_bar_sync(1, TC_SOFTMAX);
-    l = (lbuf[r] + lbuf[128 + r]) + (lbuf[256 + r] + lbuf[384 + r]);
+    if (rep) {  // a row's sum is spread over the four parts in each of the four quarters
+      l = 0.f;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4)
+        l += (lbuf[rr + 32 * q4] + lbuf[128 + rr + 32 * q4]) + (lbuf[256 + rr + 32 * q4] + lbuf[384 + rr + 32 * q4]);
+    } else {
+      l = (lbuf[r] + lbuf[128 + r]) + (lbuf[256 + r] + lbuf[384 + r]);
+    }
     if (n_tiles > 0) {
       wait_or_flag(b_pfree + 8 * g_last, ((n_tiles - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
       tc_fence_after();
@@ -520,7 +585,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     const long long ooff = static_cast<long long>(s.q0 + tq) * p.o_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.o_s1 +
                            part * (HD / 4);
 #pragma unroll 1
-    for (int c0 = 0; c0 < HD / 4; c0 += 32) {
+    for (int c0 = 0; c0 < (owns_o ? HD / 4 : 0); c0 += 32) {
       uint32_t v[32];
       if (n_tiles > 0 && !bad) {
         tmem_ld32(lane_base + C::O_COL + part * (HD / 4) + c0, v);
@@ -544,7 +609,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         }
       }
     }
-    if (valid && part == 0 && p.lse != nullptr) {
+    if (valid && owns_o && part == 0 && p.lse != nullptr) {
       p.lse[static_cast<long long>(s.h * p.gqa + hq) * p.total_q + s.q0 + tq] =
           l > 0.f ? (m_fin + lg2(l) - TC_SHIFT) * 0.6931471805599453f : -INFINITY;
     }
