@@ -457,6 +457,17 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       // both parts publish their maximum rounded UP to bf16 and take the larger (a slightly high running max
       // only makes P a little smaller)
       mxbuf[(g * 2 + hf) * 128 + r] = __float2bfloat16_ru(mx);
+      // What does not depend on the partner's maximum is fetched before the exchange barrier, so that these
+      // round trips overlap the wait for the slowest warp of the group: the running max after tile t - 1 from the
+      // other group, and the P buffer of this group (free once the PV MMAs of tile t - 2 are done; the residual
+      // flag of this tile is complete by then, every vote having preceded its thread's arrival for that tile).
+      float m_prev = -INFINITY;
+      if (t >= 1) {
+        wait_or_flag(b_mpub + 8 * (g ^ 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
+        m_prev = mrun[(g ^ 1) * 128 + r];
+      }
+      if (t >= 2) wait_or_flag(b_pfree + 8 * g, (u - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      const bool with_lo = lo_flag[g * 2 + (u & 1)] != 0u;
       named_bar_sync(grp_bar, TC_GROUP);
       if (rep) {  // eight shares of a row: two parts in each of the four quarters
         mx = -INFINITY;
@@ -466,12 +477,6 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
                                __bfloat162float(mxbuf[(g * 2 + 1) * 128 + rr + 32 * q4])));
       } else {
         mx = fmaxf(__bfloat162float(mxbuf[(g * 2) * 128 + r]), __bfloat162float(mxbuf[(g * 2 + 1) * 128 + r]));
-      }
-      // the running max after tile t - 1, from the other group
-      float m_prev = -INFINITY;
-      if (t >= 1) {
-        wait_or_flag(b_mpub + 8 * (g ^ 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
-        m_prev = mrun[(g ^ 1) * 128 + r];
       }
       float m_new = m_prev, alpha = 1.f;  // alpha: what O (relative to m_prev) is multiplied by
       if (mx > m_prev + TC_LAZY || (m_prev == -INFINITY && mx > -INFINITY)) {
@@ -485,9 +490,6 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         m_seen = m_new;
       }
       const float sh = TC_SHIFT - (m_new == -INFINITY ? 0.f : m_new);
-      // The P buffer of this group is free once the PV MMAs of tile t-2 are done.
-      if (t >= 2) wait_or_flag(b_pfree + 8 * g, (u - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
-      const bool with_lo = lo_flag[g * 2 + (u & 1)] != 0u;
       // pass 2: P = 2^(s - m + 7), e4m3 (plus the residual term while needed), into the swizzled A tiles
       if (warp_live) {
         const uint32_t p_hi = sP + (g * 2) * C::P_BYTES + rr * 128, p_lo = p_hi + C::P_BYTES;
