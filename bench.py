@@ -317,7 +317,11 @@ def main():
     attn_decode.ensure_ready(dev)
     hbm_gbs, peak_kind = peaks()
 
-    kw = W.c2_production_decode(dev, seed=2 + rank, batch=args.batch)
+    # Weak scaling: per-GPU work is fixed as N grows, so every rank serves the same draw of context lengths (the
+    # one the N = 1 line is quoted on) with its own data and page placement (seed 2 + rank).
+    g_len = torch.Generator().manual_seed(2)
+    lens = torch.randint(1024, 32769, (args.batch,), generator=g_len).tolist()
+    kw = W.c2_production_decode(dev, seed=2 + rank, batch=args.batch, lens=lens)
     nbytes = W.attn_kv_bytes(kw)
     run = attn_decode.select(kw)
     if not callable(run):
@@ -395,7 +399,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "requests_per_gpu": args.batch, "kv_tokens_rank0": nbytes // 2048,
-                       "partitioning": f"requests x{world}", "l2": "inputs (4.4 GB/GPU) larger than the 126 MB L2"},
+                       "partitioning": f"requests x{world}, same context-length draw on every rank", "l2": "inputs (4.4 GB/GPU) larger than the 126 MB L2"},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms_total / args.steps},
