@@ -1161,20 +1161,32 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
   const int c0 = cta_of(u0), c1 = cta_of(u1 - 1);
   if (c0 == c1) return;
   const int slot0 = 2 * c0 + (u0 <= slice_start(T, G, c0) ? 0 : 1);
+  // The workspace slot of every CTA that holds a piece of this unit, worked out once (a long sequence at a small
+  // batch is cut into dozens of slices; the slice bounds cost a 64-bit division each).
+  constexpr int MAX_LIST = 1024;
+  __shared__ int slot_list[MAX_LIST];
+  const int n_list = c1 - c0 + 1 <= MAX_LIST ? c1 - c0 + 1 : MAX_LIST;  // grids here stay far below the bound
+  for (int i = threadIdx.x; i < n_list; i += blockDim.x) {
+    const int c = c0 + i;
+    const bool empty = slice_start(T, G, c + 1) == slice_start(T, G, c);  // a CTA with an empty slice wrote nothing
+    slot_list[i] = empty ? -1 : (c == c0 ? slot0 : 2 * c);
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < rows * (HD / 4); idx += blockDim.x) {
     int r = idx / (HD / 4), d = (idx - r * (HD / 4)) * 4;
     float mx = -INFINITY;
-    for (int c = c0; c <= c1; ++c) {
-      if (slice_start(T, G, c + 1) == slice_start(T, G, c)) continue;  // a CTA with an empty slice wrote nothing
-      int slot = c == c0 ? slot0 : 2 * c;
-      mx = fmaxf(mx, __ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + r));
+#pragma unroll 4
+    for (int i = 0; i < n_list; ++i) {
+      const int slot = slot_list[i];
+      if (slot >= 0) mx = fmaxf(mx, __ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + r));
     }
     float den = 0.f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     if (mx != -INFINITY) {
-      for (int c = c0; c <= c1; ++c) {
-        if (slice_start(T, G, c + 1) == slice_start(T, G, c)) continue;
-        int slot = c == c0 ? slot0 : 2 * c;
+#pragma unroll 4
+      for (int i = 0; i < n_list; ++i) {
+        const int slot = slot_list[i];
+        if (slot < 0) continue;
         float w = ex2(__ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + r) - mx);
         float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (static_cast<long long>(slot) * rows_cap + r) * HD + d));
         den += w;
