@@ -13,11 +13,11 @@ import threading
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib", "libgreen_attention.so")
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 EXPORTS = (
     "ga_init", "ga_attn_workspace_bytes", "ga_attn_decode", "ga_attn_extend", "ga_attn_decode_noalloc", "ga_attn_merge",
-    "ga_gdn_recurrent", "ga_gdn_verify", "ga_fp8_tensor_peak", "ga_last_launch_count", "ga_attn_workspace_status", "ga_last_error",
+    "ga_gdn_recurrent", "ga_gdn_verify", "ga_fp8_tensor_peak", "ga_last_launch_count", "ga_attn_workspace_status", "ga_attn_workspace_clear_status", "ga_last_error",
     "ga_abi_version", "ga_sm_count",
 )
 
@@ -47,7 +47,7 @@ class GaAttnParams(ctypes.Structure):
 
 class GaMergeParams(ctypes.Structure):
     _fields_ = [
-        ("o_parts", c_void_p), ("lse_parts", c_void_p),
+        ("o_parts", c_void_p), ("lse_parts", c_void_p), ("o_part_stride", c_int64), ("lse_part_stride", c_int64),
         ("parts", c_int32), ("rows", c_int32), ("head_dim", c_int32),
         ("out", c_void_p), ("lse", c_void_p),
     ]
@@ -125,6 +125,8 @@ def lib() -> ctypes.CDLL:
         handle.ga_last_launch_count.restype = c_int
         handle.ga_attn_workspace_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
         handle.ga_attn_workspace_status.restype = c_int
+        handle.ga_attn_workspace_clear_status.argtypes = [c_void_p, c_void_p]
+        handle.ga_attn_workspace_clear_status.restype = c_int
         handle.ga_last_error.argtypes = []
         handle.ga_last_error.restype = c_char_p
         handle.ga_abi_version.argtypes = []

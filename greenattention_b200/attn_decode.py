@@ -22,6 +22,7 @@ survives only as the host-side bound the reference exposes (``attn_decode.py:123
 from __future__ import annotations
 
 import ctypes
+import logging
 import os
 from typing import Callable, Optional, Union
 
@@ -46,6 +47,13 @@ _ALLOWED = frozenset(
     )
 )
 FP8 = torch.float8_e4m3fn
+logger = logging.getLogger(__name__)
+
+STATUS_NAMES = {
+    1: "a bounded wait for a full ring stage ran out", 2: "a bounded wait for a free ring stage ran out",
+    3: "a page id was out of range", 4: "a bounded wait for tensor memory ran out",
+    5: "a cache_seqlens entry exceeded page_table.shape[1] * page_size",
+}
 
 
 class _State:
@@ -81,15 +89,44 @@ def workspace(device: torch.device) -> torch.Tensor:
     return _S.workspaces[device.index]
 
 
-def workspace_status(device: torch.device) -> int:
-    """Status word the kernels leave behind (0 = fine). Synchronises the current stream."""
-    ws = workspace(device)
+def workspace_status(device: torch.device, builtin: bool = False) -> int:
+    """Status word the kernels leave behind (0 = fine; see ``STATUS_NAMES``). It is sticky: one read covers every
+    call since the last ``clear_status``. ``builtin`` reads the word of the array ``decode_noalloc`` works on
+    (that entry point clears it at the start of each call). Synchronises the current stream."""
     val = ctypes.c_int(0)
-    _C.check(
-        _C.lib().ga_attn_workspace_status(ws.data_ptr(), torch.cuda.current_stream(device).cuda_stream, ctypes.byref(val)),
-        "ga_attn_workspace_status",
-    )
+    with torch.cuda.device(device):
+        _C.check(
+            _C.lib().ga_attn_workspace_status(
+                None if builtin else workspace(device).data_ptr(), torch.cuda.current_stream(device).cuda_stream,
+                ctypes.byref(val)),
+            "ga_attn_workspace_status",
+        )
     return val.value
+
+
+def clear_status(device: torch.device) -> None:
+    with torch.cuda.device(device):
+        _C.check(
+            _C.lib().ga_attn_workspace_clear_status(
+                workspace(device).data_ptr(), torch.cuda.current_stream(device).cuda_stream),
+            "ga_attn_workspace_clear_status",
+        )
+
+
+def check_status(device: Union[torch.device, None] = None, reset: bool = True) -> int:
+    """Read the status word, log a non-zero value as an error and (by default) clear it. The launch path never
+    synchronises, so a serving loop calls this at points where a sync is cheap: ``dispatch.prewarm`` does, and a
+    scheduler may between batches. Returns the value read."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.index not in _S.workspaces:
+        return 0
+    val = workspace_status(dev)
+    if val != 0:
+        logger.error("green_attention: kernel status %d on %s: %s; outputs of calls since the last check are "
+                     "not trustworthy", val, dev, STATUS_NAMES.get(val, "unknown"))
+        if reset:
+            clear_status(dev)
+    return val
 
 
 def fp8_tensor_peak_tflops(device: Union[torch.device, None] = None) -> float:
@@ -106,6 +143,7 @@ def fp8_tensor_peak_tflops(device: Union[torch.device, None] = None) -> float:
 
 def _prewarm(backend) -> None:
     ensure_ready()
+    check_status()
 
 
 def plan_splits(batch: int, max_ctx: int, sm_count: int = 148, units: int = 8, windowed: bool = False) -> int:
@@ -166,6 +204,12 @@ def _paged_reason(kw: dict) -> Optional[str]:
     q, kc, vc = kw["q"], kw["k_cache"], kw["v_cache"]
     pt, cs, cu = kw["page_table"], kw["cache_seqlens"], kw["cu_seqlens_q"]
     hd, kvh = q.shape[2], kc.shape[2]
+    # The C ABI takes raw addresses: a tensor on the host or on another GPU would be an illegal address in the
+    # kernel, so every tensor argument must live where q lives.
+    for name in ("k_cache", "v_cache", "page_table", "cache_seqlens", "cu_seqlens_q", "k_descale", "v_descale", "out"):
+        t = kw.get(name)
+        if isinstance(t, torch.Tensor) and t.device != q.device:
+            return f"{name} is on {t.device}, q on {q.device}"
     if q.dtype not in (FP8, torch.bfloat16):
         return f"q dtype {q.dtype}"
     if kc.dtype != FP8 or vc.dtype != FP8:
@@ -263,14 +307,17 @@ def select_extend(kw: dict) -> Union[Callable, str]:
 
 def _run(
     kind: str, *, q, k_cache, v_cache, page_table, cache_seqlens, cu_seqlens_q, max_seqlen_q, window_left=-1,
-    softmax_scale=None, return_softmax_lse=False, out=None, k_descale=None, v_descale=None, _out_f32=False, **_,
+    softmax_scale=None, return_softmax_lse=False, out=None, k_descale=None, v_descale=None, _out_f32=False,
+    _lse=None, **_,
 ):
     dev = q.device
     ws = _S.workspaces[dev.index]
     total_q, qh, hd = q.shape
     if out is None:
         out = torch.empty(q.shape, dtype=torch.float32 if _out_f32 else torch.bfloat16, device=dev)
-    lse = torch.empty((qh, total_q), dtype=torch.float32, device=dev) if return_softmax_lse else None
+    lse = _lse
+    if lse is None and return_softmax_lse:
+        lse = torch.empty((qh, total_q), dtype=torch.float32, device=dev)
     p = _C.GaAttnParams()
     p.q = q.data_ptr()
     p.q_is_bf16 = int(q.dtype == torch.bfloat16)
@@ -306,7 +353,8 @@ def _run(
     lib = _C.lib()
     fn = {"decode": lib.ga_attn_decode, "extend": lib.ga_attn_extend,
           "decode_noalloc": lib.ga_attn_decode_noalloc}[kind]
-    _C.check(fn(ctypes.byref(p), stream), f"ga_attn_{kind}")
+    with torch.cuda.device(dev):  # the library launches on the current device
+        _C.check(fn(ctypes.byref(p), stream), f"ga_attn_{kind}")
     return (out, lse) if return_softmax_lse else out
 
 
@@ -322,34 +370,62 @@ def decode_noalloc(**kw):
     return _run("decode_noalloc", window_left=wl, **{k: v for k, v in kw.items() if k != "window_size"})
 
 
-def decode_partial(**kw):
+def decode_partial(into: Optional[torch.Tensor] = None, **kw):
     """Decode over this device's shard of one request's KV range: returns ``(o fp32 [total_q, QH, HD]
     normalised, lse fp32 [QH, total_q])`` for ``merge_partials`` (the per-GPU step of a sequence whose KV
-    range is split across GPUs)."""
+    range is split across GPUs). One query token per request and no window: the kernel places the causal
+    diagonal and a window relative to the keys it is given, which is only right for a whole sequence.
+
+    ``into``: a contiguous fp32 buffer of ``total_q * QH * (HD + 1)`` elements that receives O followed by the
+    LSE (the packed form the exchange sends); the returned tensors are views of it, so nothing is copied
+    between the kernel and the collective."""
+    kw = {k: v for k, v in kw.items() if k != "out"}
     fn = select(kw)
     if not callable(fn):
         raise dispatch.Declined(f"decode_partial: {fn}")
+    wl = _window_left(kw)
+    if isinstance(wl, str) or wl >= 0:
+        raise dispatch.Declined("decode_partial: a left window cannot be applied to a KV-range shard")
+    q = kw["q"]
+    if kw["max_seqlen_q"] != 1 or q.shape[0] != kw["cache_seqlens"].shape[0]:
+        raise dispatch.Declined("decode_partial: one query token per request")
+    out = lse = None
+    if into is not None:
+        tq, qh, hd = q.shape
+        if (into.dtype != torch.float32 or into.dim() != 1 or into.numel() != tq * qh * (hd + 1)
+                or not into.is_contiguous() or into.device != q.device or into.data_ptr() % 16):
+            raise dispatch.Declined("decode_partial: `into` must be a 16-byte aligned fp32 buffer of total_q*QH*(HD+1) elements on q's device")
+        out = into[: tq * qh * hd].view(tq, qh, hd)
+        lse = into[tq * qh * hd:].view(qh, tq)
     kw = dict(kw, return_softmax_lse=True)
-    kw.pop("out", None)
-    return _run("decode", window_left=-1, _out_f32=True, **kw)
+    return _run("decode", window_left=-1, _out_f32=True, out=out, _lse=lse, **kw)
 
 
 def merge_partials(o_parts: torch.Tensor, lse_parts: torch.Tensor, return_lse: bool = False):
     """LSE-weighted merge of ``o_parts [parts, rows, HD]`` fp32 / ``lse_parts [parts, rows]`` (natural log),
-    all resident on this device, into bf16 ``[rows, HD]`` (math of ``kernel.cuh:665-749``)."""
-    o_parts = o_parts.contiguous()
-    lse_parts = lse_parts.contiguous()
+    all resident on this device, into bf16 ``[rows, HD]`` (math of ``kernel.cuh:665-749``). The tensors may be
+    strided in their first dimension (views of one gathered buffer of packed partials are read where they are);
+    the other dimensions must be dense."""
     parts, rows, hd = o_parts.shape
+    if o_parts.stride(2) != 1 or o_parts.stride(1) != hd or o_parts.dtype != torch.float32:
+        o_parts = o_parts.float().contiguous()
+    if lse_parts.stride(1) != 1 or lse_parts.dtype != torch.float32:
+        lse_parts = lse_parts.float().contiguous()
+    if lse_parts.device != o_parts.device or not o_parts.is_cuda:
+        raise dispatch.Declined("merge_partials: partials must be CUDA tensors on one device")
     out = torch.empty((rows, hd), dtype=torch.bfloat16, device=o_parts.device)
     lse = torch.empty((rows,), dtype=torch.float32, device=o_parts.device) if return_lse else None
     m = _C.GaMergeParams()
     m.o_parts, m.lse_parts = o_parts.data_ptr(), lse_parts.data_ptr()
+    m.o_part_stride = o_parts.stride(0) if parts > 1 else 0
+    m.lse_part_stride = lse_parts.stride(0) if parts > 1 else 0
     m.parts, m.rows, m.head_dim = parts, rows, hd
     m.out = out.data_ptr()
     m.lse = lse.data_ptr() if lse is not None else None
-    _C.check(
-        _C.lib().ga_attn_merge(ctypes.byref(m), torch.cuda.current_stream(o_parts.device).cuda_stream), "ga_attn_merge"
-    )
+    with torch.cuda.device(o_parts.device):
+        _C.check(
+            _C.lib().ga_attn_merge(ctypes.byref(m), torch.cuda.current_stream(o_parts.device).cuda_stream), "ga_attn_merge"
+        )
     return (out, lse) if return_lse else out
 
 

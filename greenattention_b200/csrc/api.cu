@@ -181,6 +181,16 @@ int set_smem(const AttnInstance& k) {
   return 0;
 }
 
+// Raises the dynamic shared memory limit of every kernel instance on the current device.
+int set_all_smem_limits() {
+  for (int hd : {128, 256}) {
+    for (int rows : {8, 16, 24, 32, 64, 128})
+      if (set_smem(*decode_instance(hd, rows))) return 1;
+    if (set_smem(*extend_instance(hd)) || set_smem(*extend_tc_instance(hd)) || set_smem(*verify_tc_instance(hd))) return 1;
+  }
+  return 0;
+}
+
 constexpr size_t kWsHeader = 256;
 size_t ws_prefix_bytes(int batch) { return ((static_cast<size_t>(batch) + 1) * 4 + 255) / 256 * 256; }
 size_t ws_lse_bytes(int sm) { return static_cast<size_t>(2 * sm) * ga::attn::MAX_ROWS * 4; }
@@ -271,22 +281,44 @@ int launch_gdn(const ga::gdn::GdnDev& d, bool bf16_state, int blocks, cudaStream
   return 0;
 }
 
-__global__ void merge_parts_kernel(const float* o_parts, const float* lse_parts, int parts, int rows, int hd,
-                                   __nv_bfloat16* out, float* lse) {
+// One CTA per row; thread d owns output dims d, d + blockDim, ...; the parts are folded in index order by every
+// thread, so the result does not depend on scheduling.
+__global__ void merge_parts_kernel(const float* o_parts, const float* lse_parts, long long o_ps, long long l_ps,
+                                   int parts, int rows, int hd, __nv_bfloat16* out, float* lse) {
   const int r = blockIdx.x;
   float mx = -INFINITY;
-  for (int s = 0; s < parts; ++s) mx = fmaxf(mx, lse_parts[s * rows + r]);
+  for (int s = 0; s < parts; ++s) mx = fmaxf(mx, lse_parts[s * l_ps + r]);
   float den = 0.f;
   if (mx != -INFINITY)
-    for (int s = 0; s < parts; ++s) den += expf(lse_parts[s * rows + r] - mx);
+    for (int s = 0; s < parts; ++s) den += expf(lse_parts[s * l_ps + r] - mx);
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.f;
     if (mx != -INFINITY)
       for (int s = 0; s < parts; ++s)
-        acc += expf(lse_parts[s * rows + r] - mx) * o_parts[(static_cast<long long>(s) * rows + r) * hd + d];
+        acc += expf(lse_parts[s * l_ps + r] - mx) * o_parts[s * o_ps + static_cast<long long>(r) * hd + d];
     out[static_cast<long long>(r) * hd + d] = __float2bfloat16(den > 0.f ? acc / den : 0.f);
   }
   if (lse && threadIdx.x == 0) lse[r] = den > 0.f ? mx + logf(den) : -INFINITY;
+}
+
+// Body of ga_init with `device` current; the caller restores the previous device whatever this returns.
+int init_current_device(int device) {
+  cudaDeviceProp prop;
+  GA_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail("device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    GA_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || !fn) return fail("cuTensorMapEncodeTiled is not available");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  if (set_all_smem_limits()) return 1;
+  std::lock_guard<std::mutex> lock(g_mu);
+  g_dev[device].sm_count = prop.multiProcessorCount;
+  g_dev[device].ready = true;
+  return 0;
 }
 
 }  // namespace
@@ -306,28 +338,10 @@ int ga_init(int device) {
   int prev = 0;
   GA_CUDA(cudaGetDevice(&prev));
   GA_CUDA(cudaSetDevice(device));
-  cudaDeviceProp prop;
-  GA_CUDA(cudaGetDeviceProperties(&prop, device));
-  if (prop.major != 10) {
-    cudaSetDevice(prev);
-    return fail("device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
-  }
-  if (!g_encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    GA_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
-    if (qres != cudaDriverEntryPointSuccess || !fn) return fail("cuTensorMapEncodeTiled is not available");
-    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-  }
-  for (int hd : {128, 256}) {
-    for (int rows : {8, 16, 24, 32, 64, 128})
-      if (set_smem(*decode_instance(hd, rows))) return 1;
-    if (set_smem(*extend_instance(hd)) || set_smem(*extend_tc_instance(hd)) || set_smem(*verify_tc_instance(hd))) return 1;
-  }
-  GA_CUDA(cudaSetDevice(prev));
-  std::lock_guard<std::mutex> lock(g_mu);
-  g_dev[device].sm_count = prop.multiProcessorCount;
-  g_dev[device].ready = true;
+  const int rc = init_current_device(device);
+  const cudaError_t back = cudaSetDevice(prev);  // also on the error paths: the caller's device stays current
+  if (rc) return rc;
+  if (back != cudaSuccess) return fail("cudaSetDevice(%d) failed: %s", prev, cudaGetErrorString(back));
   return 0;
 }
 
@@ -480,8 +494,11 @@ int ga_attn_extend(const GaAttnParams* a, void* stream) {
 int ga_attn_merge(const GaMergeParams* m, void* stream) {
   if (!m || !m->o_parts || !m->lse_parts || !m->out) return fail("null params");
   if (m->parts <= 0 || m->rows <= 0 || m->head_dim <= 0) return fail("bad merge shape");
+  if (m->o_part_stride < 0 || m->lse_part_stride < 0) return fail("negative part stride");
+  const long long o_ps = m->o_part_stride ? m->o_part_stride : static_cast<long long>(m->rows) * m->head_dim;
+  const long long l_ps = m->lse_part_stride ? m->lse_part_stride : m->rows;
   merge_parts_kernel<<<m->rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      m->o_parts, m->lse_parts, m->parts, m->rows, m->head_dim, static_cast<__nv_bfloat16*>(m->out), m->lse);
+      m->o_parts, m->lse_parts, o_ps, l_ps, m->parts, m->rows, m->head_dim, static_cast<__nv_bfloat16*>(m->out), m->lse);
   GA_CUDA(cudaGetLastError());
   g_launches = 1;
   return 0;
@@ -640,10 +657,33 @@ int ga_fp8_tensor_peak(void* status_word, void* stream, float* tflops) {
   return 0;
 }
 
+// The status word of `workspace`, or of the array ga_attn_decode_noalloc works on when `workspace` is NULL
+// (NULL before that entry point's first call on the current device reads as an error).
+static int status_word_address(const void* workspace, const int** word) {
+  if (workspace) {
+    *word = static_cast<const int*>(workspace);
+    return 0;
+  }
+  int dev;
+  if (current_device(&dev)) return 1;
+  if (g_noalloc_ptr[dev] == nullptr) return fail("ga_attn_decode_noalloc has not run on device %d", dev);
+  *word = reinterpret_cast<const int*>(g_noalloc_ptr[dev]);
+  return 0;
+}
+
 int ga_attn_workspace_status(const void* workspace, void* stream, int* status) {
-  if (!workspace || !status) return fail("null pointer");
-  GA_CUDA(cudaMemcpyAsync(status, workspace, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  if (!status) return fail("null pointer");
+  const int* word;
+  if (status_word_address(workspace, &word)) return 1;
+  GA_CUDA(cudaMemcpyAsync(status, word, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
   GA_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return 0;
+}
+
+int ga_attn_workspace_clear_status(void* workspace, void* stream) {
+  const int* word;
+  if (status_word_address(workspace, &word)) return 1;
+  GA_CUDA(cudaMemsetAsync(const_cast<int*>(word), 0, sizeof(int), static_cast<cudaStream_t>(stream)));
   return 0;
 }
 

@@ -77,9 +77,21 @@ struct AttnDev {
 struct SeqInfo {
   int L, ql, tlo, cnt;
 };
+// Keys of request b. A length beyond what the page-table row can address (a caller error that live lengths
+// under graph replay can produce) is cut to the addressable range and recorded in the status word, so neither
+// gather path ever indexes past the row.
+__device__ __forceinline__ int seq_len_checked(const AttnDev& p, int b) {
+  int L = p.seqlens[b];
+  const long long cap = static_cast<long long>(p.pt_cols) << p.page_shift;
+  if (L > cap) {
+    L = static_cast<int>(cap);
+    atomicExch(p.status, GA_ST_LEN_RANGE);
+  }
+  return L;
+}
 __device__ __forceinline__ SeqInfo seq_info(const AttnDev& p, int b) {
   SeqInfo s;
-  s.L = p.seqlens[b];
+  s.L = seq_len_checked(p, b);
   int ql = p.cu[b + 1] - p.cu[b];
   s.ql = ql < p.max_q ? ql : p.max_q;
   if (s.L <= 0 || s.ql <= 0) {
@@ -239,7 +251,7 @@ __device__ __forceinline__ bool extend_block(const AttnDev& p, int x_in, int h, 
   one.h = h;
   one.q0 = p.cu[b] + j * p.bq;
   one.nq = min(p.bq, ql - j * p.bq);
-  one.L = p.seqlens[b];
+  one.L = seq_len_checked(p, b);
   one.pos0 = one.L - ql + j * p.bq;
   int last = one.pos0 + one.nq - 1;
   if (last > one.L - 1) last = one.L - 1;

@@ -12,7 +12,10 @@
 namespace ga {
 
 // Status word values a kernel may leave in the workspace header (0 = fine).
-enum : int { GA_ST_OK = 0, GA_ST_WAIT_FULL = 1, GA_ST_WAIT_EMPTY = 2, GA_ST_BAD_PAGE = 3, GA_ST_WAIT_TMEM = 4 };
+enum : int {
+  GA_ST_OK = 0, GA_ST_WAIT_FULL = 1, GA_ST_WAIT_EMPTY = 2, GA_ST_BAD_PAGE = 3, GA_ST_WAIT_TMEM = 4,
+  GA_ST_LEN_RANGE = 5  // a cache_seqlens entry exceeds pt_cols * page_size
+};
 
 // Upper bound on polls of one barrier wait. A poll of try_wait may itself block for a
 // hardware-defined interval, so this bounds a stuck wait to seconds, after which the kernel records

@@ -10,6 +10,7 @@ sm_100 device are wrapped. SGLang is imported lazily so the module loads (and is
 from __future__ import annotations
 
 import logging
+import os
 
 import torch
 
@@ -81,10 +82,25 @@ class GreenGDNKernel(_kernel_base()):
         return self.fallback.extend(q, k, v, g, beta, **kwargs)
 
 
+# Without an SGLang runtime context (a benchmark, a test, another host program calling the GDN front-end
+# directly) nothing can say which attention backend the server runs; such callers declare themselves with
+# ``set_standalone(True)`` or ``GREEN_ATTN_STANDALONE=1`` and only the device check remains.
+_standalone = os.environ.get("GREEN_ATTN_STANDALONE", "0") == "1"
+
+
+def set_standalone(on: bool = True) -> None:
+    global _standalone
+    _standalone = bool(on)
+
+
 def _green_on_sm100() -> bool:
+    if not torch.cuda.is_available() or torch.cuda.get_device_capability()[0] != 10:
+        return False
+    if _standalone:
+        return True
     from sglang.srt.runtime_context import attention_backends
 
-    return "green" in attention_backends() and torch.cuda.get_device_capability()[0] == 10
+    return "green" in attention_backends()
 
 
 def gdn_init_around(original, self, *args, **kwargs):

@@ -30,6 +30,13 @@ import torch
 
 from greenattention_b200 import _C, dispatch
 
+# Names this module expects SGLang to define (file under python/sglang/ -> symbols); the hook itself is
+# registered by ``plugin.register``.
+SGLANG_READS = {
+    "srt/plugins/hook_registry.py": ("HookRegistry", "HookType", "AROUND"),
+    "kernels/ops/attention/linear/gdn_replayssm_spec_decode.py": ("gdn_replayssm_spec_decode",),
+}
+
 K = V = 128
 MAX_SPEC = 8
 _ready: set = set()
@@ -83,14 +90,37 @@ def _launch(
     p.batch, p.tokens, p.h, p.hv, p.k_dim, p.v_dim = batch, tokens, h, hv, K, V
     p.l2norm_qk, p.round_beta_bf16, p.pad_reads_zero = int(l2norm), int(round_beta), int(pad_reads_zero)
     p.scale = float(K**-0.5 if scale is None else scale)
-    _C.check(
-        _C.lib().ga_gdn_recurrent(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream), "ga_gdn_recurrent"
-    )
+    _require_cuda(q)
+    bad_dev = _device_reason(q, dict(out=out, accept_lens=accept, query_start_loc=qsl))
+    if bad_dev:
+        raise dispatch.Declined(f"gdn: {bad_dev}")
+    with torch.cuda.device(q.device):  # the library launches on the current device
+        _C.check(
+            _C.lib().ga_gdn_recurrent(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream), "ga_gdn_recurrent"
+        )
     return out
+
+
+def _device_reason(anchor: torch.Tensor, tensors: dict) -> Optional[str]:
+    """The C ABI takes raw addresses and launches on ``anchor``'s device, so every tensor must live there (a
+    length or index tensor left on the host would be an illegal address inside the kernel). Selectors look at
+    placement only relative to ``anchor``; the launchers refuse host tensors outright (``_require_cuda``)."""
+    for name, t in tensors.items():
+        if isinstance(t, torch.Tensor) and t.device != anchor.device:
+            return f"{name} is on {t.device}, expected {anchor.device}"
+    return None
+
+
+def _require_cuda(t: torch.Tensor) -> None:
+    if not t.is_cuda:
+        raise _C.GreenAttentionError(f"tensors are on {t.device}: the green kernels have no CPU path")
 
 
 def _common_reasons(q, k, v, a, b, A_log, dt_bias, state, idx, hv) -> list:
     why = []
+    bad_dev = _device_reason(q, dict(k=k, v=v, a=a, b=b, A_log=A_log, dt_bias=dt_bias, ssm_states=state, cache_indices=idx))
+    if bad_dev:
+        why.append(bad_dev)
     if any(t.dtype is not torch.bfloat16 for t in (q, k, v)):
         why.append("q/k/v dtype")
     if a.dtype is not torch.bfloat16 or b.dtype is not torch.bfloat16:
@@ -349,6 +379,11 @@ def _verify_supported(call) -> Optional[str]:
     out = call.get("out")
     if not isinstance(out, torch.Tensor) or out.dtype is not torch.bfloat16 or out.shape[0] != T:
         return "out must be bf16 [T, HV, V]"
+    bad_dev = _device_reason(q, {n: call.get(n) for n in (
+        "k", "v", "a", "b", "A_log", "dt_bias", "checkpoint_state", "d_cache", "rawv_cache", "k_cache", "rawk_cache",
+        "g_cache", "ssm_state_indices", "replay_indices", "query_start_loc", "write_pos", "cache_base", "is_flush", "out")})
+    if bad_dev:
+        return bad_dev
     if out.ndim == 3:
         if tuple(out.shape[1:]) != (hv, V) or out.stride(2) != 1 or out.stride(1) != V:
             return f"out layout {tuple(out.shape)} {out.stride()}"
@@ -359,6 +394,7 @@ def _verify_supported(call) -> Optional[str]:
 
 def _run_verify(call) -> torch.Tensor:
     """Launch the Replay-SSM verify kernel on a call that ``_verify_supported`` accepted."""
+    _require_cuda(call["q"])
     ensure_ready(call["q"].device)
     q, st, out = call["q"], call["checkpoint_state"], call["out"]
     p = _C.GaGdnVerifyParams()
@@ -382,7 +418,8 @@ def _run_verify(call) -> torch.Tensor:
     p.h = q.shape[1] if q.ndim == 3 else q.shape[-1] // K
     p.k_dim, p.v_dim, p.ring_len = K, V, int(call["max_cache_len"])
     p.scale = K**-0.5 if call.get("scale") is None else float(call["scale"])
-    _C.check(_C.lib().ga_gdn_verify(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream), "ga_gdn_verify")
+    with torch.cuda.device(q.device):  # the library launches on the current device
+        _C.check(_C.lib().ga_gdn_verify(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream), "ga_gdn_verify")
     return out
 
 

@@ -60,6 +60,7 @@ def decode_kv_sharded(
     ``partial_fn(**local_kw) -> (o [1, QH, HD] fp32, lse [QH, 1])`` and ``merge_fn(o_parts, lse_parts) -> out``
     default to the CUDA entry points; tests of the exchange logic on CPU pass stand-ins.
     """
+    default_kernels = partial_fn is None
     if partial_fn is None or merge_fn is None:
         from greenattention_b200 import attn_decode
 
@@ -70,12 +71,19 @@ def decode_kv_sharded(
         raise ValueError("decode_kv_sharded handles one query token of one sequence")
     qh, hd = q.shape[1], q.shape[2]
     world = dist.get_world_size(group) if dist.is_initialized() else 1
-    o, lse = partial_fn(**local_kw)
-    mine = pack_partial(o[0], lse[:, 0])
+    n = qh * (hd + 1)
+    if default_kernels:
+        # The kernel writes O and LSE straight into this rank's slot of the packed send buffer and the merge kernel
+        # reads the gathered buffer where it landed: no copy kernels between the decode, the collective and the merge.
+        mine = torch.empty(n, dtype=torch.float32, device=q.device)
+        partial_fn(into=mine, **local_kw)
+    else:
+        o, lse = partial_fn(**local_kw)
+        mine = pack_partial(o[0], lse[:, 0])
     if world == 1:
         gathered = mine
     else:
-        gathered = torch.empty(world * mine.numel(), dtype=torch.float32, device=mine.device)
+        gathered = torch.empty(world * n, dtype=torch.float32, device=mine.device)
         dist.all_gather_into_tensor(gathered, mine, group=group)
     o_parts, lse_parts = unpack_partials(gathered, world, qh, hd)
-    return merge_fn(o_parts.contiguous(), lse_parts.contiguous())
+    return merge_fn(o_parts, lse_parts)

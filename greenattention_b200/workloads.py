@@ -134,6 +134,56 @@ def case_to(kw: dict, device) -> dict:
     return out
 
 
+def extract_requests(kw: dict, requests, device="cpu") -> dict:
+    """The sub-call that holds only ``requests`` (indices into the batch) of a paged call, on ``device``, with a
+    compacted page pool: the pages those requests own are gathered in page-table order and renumbered 0, 1, ...,
+    so a multi-GB pool resident on a GPU can be checked request by request on the host without copying all of
+    it. Token order, page contents, queries and descales are untouched, so attention over the sub-call equals
+    rows ``cu[r]:cu[r+1]`` of attention over the whole call."""
+    kc, vc, pt = kw["k_cache"], kw["v_cache"], kw["page_table"]
+    page = kc.shape[1]
+    lens = kw["cache_seqlens"].tolist()
+    cu = kw["cu_seqlens_q"].tolist()
+    requests = [int(r) for r in requests]
+    ids, rows_q, new_pt_rows, qlens = [], [], [], []
+    n_new = 0
+    for r in requests:
+        npg = max(1, -(-int(lens[r]) // page))
+        ids.append(pt[r, :npg].long())
+        new_pt_rows.append(torch.arange(n_new, n_new + npg, dtype=torch.int32))
+        n_new += npg
+        rows_q.append(torch.arange(cu[r], cu[r + 1]))
+        qlens.append(cu[r + 1] - cu[r])
+    ids = torch.cat(ids).to(kc.device)
+    max_p = max(t.numel() for t in new_pt_rows) + 1
+    new_pt = torch.zeros((len(requests), max_p), dtype=torch.int32)
+    for i, t in enumerate(new_pt_rows):
+        new_pt[i, : t.numel()] = t
+    rows_q = torch.cat(rows_q) if rows_q else torch.zeros(0, dtype=torch.long)
+    new_cu = torch.zeros(len(requests) + 1, dtype=torch.int32)
+    new_cu[1:] = torch.tensor(qlens, dtype=torch.int32).cumsum(0)
+    sub = {k: v for k, v in kw.items() if not isinstance(v, torch.Tensor)}
+    sub.update(
+        q=kw["q"][rows_q.to(kw["q"].device)].to(device),
+        k_cache=kc[ids].to(device), v_cache=vc[ids].to(device),
+        page_table=new_pt.to(device),
+        cache_seqlens=torch.tensor([int(lens[r]) for r in requests], dtype=torch.int32, device=device),
+        cu_seqlens_q=new_cu.to(device), max_seqlen_q=int(max(qlens)) if qlens else 0,
+    )
+    for name in ("k_descale", "v_descale"):
+        t = kw.get(name)
+        if t is not None:
+            sub[name] = (t[torch.tensor(requests, device=t.device)] if t.shape[0] > 1 else t).to(device).contiguous()
+    sub.pop("out", None)
+    return sub
+
+
+def request_rows(kw: dict, requests) -> torch.Tensor:
+    """Row indices (dim 0 of q / out) of ``requests``, in the order ``extract_requests`` lays them out."""
+    cu = kw["cu_seqlens_q"].tolist()
+    return torch.cat([torch.arange(cu[int(r)], cu[int(r) + 1]) for r in requests])
+
+
 # ------------------------------------------------------------------ the named configurations
 
 

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define GA_ABI_VERSION 1
+#define GA_ABI_VERSION 2
 
 /* Paged FP8 attention call (decode, speculative verify, extend). Mirrors the keyword arguments the
  * reference's selectors accept (green_attention/attn_decode.py:152-258). */
@@ -72,6 +72,10 @@ typedef struct GaAttnParams {
 typedef struct GaMergeParams {
   const float* o_parts;   /* [parts, rows, head_dim] normalised partial outputs (all parts in LOCAL memory) */
   const float* lse_parts; /* [parts, rows] natural-log LSE, -inf where a part saw no key */
+  int64_t o_part_stride;  /* elements between consecutive parts of o_parts; 0 = dense (rows * head_dim) */
+  int64_t lse_part_stride;/* elements between consecutive parts of lse_parts; 0 = dense (rows). With both set to
+                             rows * (head_dim + 1) and lse_parts = o_parts + rows * head_dim the kernel reads an
+                             all-gathered buffer of packed (O, LSE) partials where it landed */
   int32_t parts, rows, head_dim;
   void* out;              /* [rows, head_dim] bf16 */
   float* lse;             /* [rows] or NULL */
@@ -176,7 +180,8 @@ int ga_attn_extend(const GaAttnParams* p, void* stream);
  * for every call); make that first call before any stream capture. All calls on a device share the one
  * array and it keeps the previous call's contents (the status word is cleared on the stream at every call,
  * everything else is rewritten before it is read), so two calls that may overlap on the GPU (different
- * streams, or different host threads without ordering) race: serialise them. */
+ * streams, or different host threads without ordering) race: serialise them. The status word of the last
+ * call is read with ga_attn_workspace_status(NULL, stream, &status). */
 int ga_attn_decode_noalloc(const GaAttnParams* p, void* stream);
 int ga_attn_merge(const GaMergeParams* p, void* stream);
 int ga_gdn_recurrent(const GaGdnParams* p, void* stream);
@@ -185,8 +190,14 @@ int ga_gdn_verify(const GaGdnVerifyParams* p, void* stream);
 /* Number of kernels the last successful call on this thread launched (bench bookkeeping). */
 int ga_last_launch_count(void);
 /* Reads the status word a kernel leaves in a decode workspace (0 = fine; non-zero = a bounded wait ran
- * out or a page id was out of range). Synchronises `stream`. */
+ * out, a page id was out of range, or a cache_seqlens entry exceeded what its page-table row can address).
+ * The word is sticky: kernels only ever set it, so one read covers every call since the last clear.
+ * `workspace` NULL reads the word of the array ga_attn_decode_noalloc works on (current device; that entry
+ * point clears its word at the start of every call, so read it after the call you care about and before the
+ * next one). Synchronises `stream`. No allocation. */
 int ga_attn_workspace_status(const void* workspace, void* stream, int* status);
+/* Sets the status word back to 0, ordered on `stream` (NULL workspace as above). No synchronisation. */
+int ga_attn_workspace_clear_status(void* workspace, void* stream);
 
 /* Measures the dense FP8 (e4m3) tensor-core issue rate of the current device with a loop of tcgen05 MMAs on
  * zeroed shared-memory operands (M 128, N 256, K 32 per instruction, every SM busy): the denominator the extend

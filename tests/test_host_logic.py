@@ -194,6 +194,39 @@ def test_valid_cpu_call_is_declined_only_for_not_being_prewarmed():
     assert attn_decode.select_extend(_cpu_case(max_seqlen_q=300)) == "kernel not prewarmed for this device"
 
 
+@pytest.mark.parametrize("stray", ["cache_seqlens", "page_table", "cu_seqlens_q", "k_descale", "out"])
+def test_tensor_on_another_device_than_q_is_declined(stray):
+    """The C ABI takes raw addresses, so a length / index tensor left on the host while q is on a device must be
+    declined by the selector, never launched. ``meta`` tensors stand in for the device here."""
+    from greenattention_b200 import attn_decode
+    from greenattention_b200 import workloads as W
+
+    kw = W.make_paged_case([300, 40], [1, 1], 16, q_heads=8, kv_heads=2, head_dim=128, seed=21, descale="rand",
+                           out_mode="given")
+    moved = {k: (v.to("meta") if isinstance(v, torch.Tensor) and k != stray else v) for k, v in kw.items()}
+    why = attn_decode.select(moved)
+    assert isinstance(why, str) and why.startswith(f"{stray} is on cpu"), why
+
+
+def test_gdn_selectors_decline_tensors_on_another_device(monkeypatch):
+    from greenattention_b200 import gdn, gdn_recurrent
+    from greenattention_b200 import workloads as W
+
+    monkeypatch.setattr(gdn, "_green_on_sm100", lambda: True)
+    c = W.make_gdn_case(2, 4, h=2, hv=4, seed=3)
+    assert callable(gdn_recurrent._select_spec(c))
+    moved = {k: (v.to("meta") if isinstance(v, torch.Tensor) and k != "cache_indices" else v) for k, v in c.items()}
+    why = gdn_recurrent._select_spec(moved)
+    assert isinstance(why, str) and "cache_indices is on cpu" in why, why
+    rc = W.make_gdn_replay_case([4, 2], h=2, hv=4, ring_len=16)
+    moved = {k: (v.to("meta") if isinstance(v, torch.Tensor) and k != "write_pos" else v) for k, v in rc.items()}
+    why = gdn_recurrent._verify_supported(moved)
+    assert isinstance(why, str) and "write_pos is on cpu" in why, why
+    with pytest.raises(Exception, match="no CPU path|no CUDA"):
+        gdn_recurrent._launch  # noqa: B018 - the launchers themselves refuse host tensors:
+        gdn_recurrent._require_cuda(c["q"])
+
+
 def test_no_cpu_path(monkeypatch):
     from greenattention_b200 import _C, attn_decode
 

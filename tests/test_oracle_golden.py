@@ -95,3 +95,21 @@ def test_host_tables_fixture_is_well_formed():
         t = json.load(f)
     assert t["ops"] == ["decode", "verify", "extend", "gdn_decode", "gdn_verify"] and t["max_verify_q"] == 16
     assert len(t["plan_splits"]) == 1152
+
+
+def test_extract_requests_gives_the_same_attention_as_the_whole_call():
+    """``workloads.extract_requests`` (the sampler the full-size GPU tests and the bench use to check part of a
+    call on the host) must not change what the oracle computes for the requests it keeps."""
+    from greenattention_b200 import workloads as W
+    from oracle import attn_oracle
+
+    kw = W.make_paged_case([300, 0, 41, 1000, 64], [2, 2, 1, 3, 2], 16, q_heads=8, kv_heads=2, head_dim=128, seed=44,
+                           descale="rand", window=(200, 0), kv_stack=True, q_strided=True)
+    whole, lse = attn_oracle.paged_attention(kw)
+    pick = [3, 0, 4]
+    sub = W.extract_requests(kw, pick)
+    part, lse_part = attn_oracle.paged_attention(sub)
+    rows = W.request_rows(kw, pick)
+    assert torch.equal(part, whole[rows])
+    assert torch.equal(lse_part, lse[:, rows])
+    assert sub["k_cache"].shape[0] == 63 + 19 + 4  # only the pages those requests own

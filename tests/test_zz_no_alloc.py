@@ -37,13 +37,35 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row():
                               seed=301, descale="rand", extra_pages=4)
     second = W.make_paged_case([3, 700, 31000], [2, 2, 2], 64, q_heads=16, kv_heads=2, head_dim=128, seed=302,
                                window=(511, 0))
-    for kw_cpu in (first, second):
+    # head_dim 256 takes other kernel instances (GQA 2 decode: the 8-row one; GQA 6 x 2 tokens: the 16-row one)
+    third = W.make_paged_case([9000, 1, 300, 0, 2500], [1] * 5, 64, q_heads=4, kv_heads=2, head_dim=256, seed=305,
+                              descale="rand", window=(1023, 0))
+    fourth = W.make_paged_case([5000, 70], [2, 2], 16, q_heads=12, kv_heads=2, head_dim=256, seed=306)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    for kw_cpu in (first, second, third, fourth):
         kw = W.case_to(kw_cpu, "cuda")
         (out, lse), (ref_out, ref_lse) = _both(kw)
         assert torch.equal(out, ref_out)
         assert torch.equal(lse, ref_lse)
+        # the status word of the built-in array is readable after the call (and says the call was clean)
+        assert attn_decode.workspace_status(dev, builtin=True) == 0
         ref_o, _ = attn_oracle.paged_attention(kw_cpu)
         assert ((out.float().cpu() - ref_o).abs() <= 2e-2 + 2e-2 * ref_o.abs()).all()
+
+
+def test_noalloc_status_word_reports_a_bad_call_until_the_next_call_clears_it():
+    from greenattention_b200 import attn_decode
+
+    attn_decode.ensure_ready()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    kw = W.case_to(W.make_paged_case([200, 64], [1, 1], 64, q_heads=8, kv_heads=2, head_dim=128, seed=307, pt_pad=0), "cuda")
+    good_lens = kw["cache_seqlens"].clone()
+    kw["cache_seqlens"] = torch.tensor([kw["page_table"].shape[1] * 64 + 1, 64], dtype=torch.int32, device="cuda")
+    attn_decode.decode_noalloc(**kw)
+    assert attn_decode.workspace_status(dev, builtin=True) == 5  # length beyond the page-table row: cut and recorded
+    kw["cache_seqlens"] = good_lens
+    attn_decode.decode_noalloc(**kw)
+    assert attn_decode.workspace_status(dev, builtin=True) == 0
 
 
 def test_noalloc_rejects_calls_beyond_its_scratch():
