@@ -376,25 +376,30 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
   d.max_q = a->max_seqlen_q;
   d.bq = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // Speculative verify (more than 16 rows per kv head) with enough (request, kv head) pairs to fill the SMs runs
-  // on the tcgen05 kernel, one CTA per pair; short batches and long contexts keep the split-KV kernel, which
-  // balances tiles across all SMs whatever the batch.
-  if (rows > 16 && !a->out_is_f32 && tc_aligned(a, d) && a->batch * a->kv_heads >= sm) {
-    d.bq = ga::attn::MAX_ROWS / d.gqa;
-    d.max_q = 1 << 30;
-    const AttnInstance* tk = rows <= 32 ? verify_tc_instance(a->head_dim) : extend_tc_instance(a->head_dim);
-    dim3 tgrid(static_cast<unsigned>(a->total_q / d.bq + a->batch), a->kv_heads);
-    tk->fn<<<tgrid, tk->threads, tk->smem, st>>>(d, kmap, vmap);
+  // Speculative verify with more than 16 rows per kv head runs on the persistent tcgen05 kernel: the same
+  // tile-stream split as the warp-level kernel (128-key tiles, one CTA per SM, partials merged by the combine
+  // kernel), so it balances at any batch.
+  if (rows > 16 && !a->out_is_f32 && tc_aligned(a, d)) {
+    const bool rep = rows <= 32;
+    const AttnInstance* tk = rep ? verify_tc_instance(a->head_dim) : extend_tc_instance(a->head_dim);
+    d.tc_mode = 0;
+    d.rows_cap = rep ? 32 : ga::attn::MAX_ROWS;
+    tk->fn<<<sm, tk->threads, tk->smem, st>>>(d, kmap, vmap);
     GA_CUDA(cudaGetLastError());
-    g_launches = 1;
+    dim3 tgrid(a->batch, a->kv_heads);
+    if (a->head_dim == 128)
+      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, tgrid, dim3(128), 0, st, d, sm, d.rows_cap, ga::attn::tc::TNK));
+    else
+      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, tgrid, dim3(128), 0, st, d, sm, d.rows_cap, ga::attn::tc::TNK));
+    g_launches = 2;
     return 0;
   }
   const AttnInstance* k = decode_instance(a->head_dim, rows);
   const int grid = sm * k->occ;
   GA_CUDA(launch_pdl(k->fn, dim3(grid), dim3(k->threads), k->smem, st, d, kmap, vmap));
   dim3 cgrid(a->batch, a->kv_heads);
-  if (a->head_dim == 128) GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, cgrid, dim3(128), 0, st, d, grid, k->rows));
-  else GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, cgrid, dim3(128), 0, st, d, grid, k->rows));
+  if (a->head_dim == 128) GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN));
+  else GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN));
   g_launches = 2;
   return 0;
 }
@@ -455,8 +460,8 @@ int ga_attn_decode_noalloc(const GaAttnParams* a, void* stream) {
   k->fn<<<grid, k->threads, k->smem, st>>>(d, kmap, vmap);
   GA_CUDA(cudaGetLastError());
   dim3 cgrid(a->batch, a->kv_heads);
-  if (a->head_dim == 128) ga::attn::attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(d, grid, k->rows);
-  else ga::attn::attn_combine_kernel<256><<<cgrid, 128, 0, st>>>(d, grid, k->rows);
+  if (a->head_dim == 128) ga::attn::attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(d, grid, k->rows, ga::attn::TN);
+  else ga::attn::attn_combine_kernel<256><<<cgrid, 128, 0, st>>>(d, grid, k->rows, ga::attn::TN);
   GA_CUDA(cudaGetLastError());
   g_launches = 2;
   return 0;
@@ -481,11 +486,23 @@ int ga_attn_extend(const GaAttnParams* a, void* stream) {
     return 0;
   }
   // The tcgen05 kernel wants TMA-sized pages and 16-byte aligned q / out rows; anything else runs on the
-  // warp-level MMA kernel.
-  const bool tc_ok = tc_aligned(a, d);
-  const AttnInstance* k = tc_ok ? extend_tc_instance(a->head_dim) : extend_instance(a->head_dim);
-  dim3 grid(static_cast<unsigned>(blocks), a->kv_heads);
-  k->fn<<<grid, k->threads, k->smem, static_cast<cudaStream_t>(stream)>>>(d, kmap, vmap);
+  // warp-level MMA kernel. The tcgen05 kernel is persistent: one CTA per SM deals itself (block, kv head) items.
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (tc_aligned(a, d)) {
+    const AttnInstance* k = extend_tc_instance(a->head_dim);
+    d.tc_mode = 1;
+    d.nblk = static_cast<int>(blocks);
+    d.rows_cap = ga::attn::MAX_ROWS;
+    const long long items = blocks * a->kv_heads;
+    if (items > 0x7fffffffLL) return fail("too many (block, kv head) items");
+    const int sm = g_dev[dev].sm_count;
+    const unsigned grid = static_cast<unsigned>(items < sm ? items : sm);
+    k->fn<<<grid, k->threads, k->smem, st>>>(d, kmap, vmap);
+  } else {
+    const AttnInstance* k = extend_instance(a->head_dim);
+    dim3 grid(static_cast<unsigned>(blocks), a->kv_heads);
+    k->fn<<<grid, k->threads, k->smem, st>>>(d, kmap, vmap);
+  }
   GA_CUDA(cudaGetLastError());
   g_launches = 1;
   return 0;
@@ -686,5 +703,19 @@ int ga_attn_workspace_clear_status(void* workspace, void* stream) {
   GA_CUDA(cudaMemsetAsync(const_cast<int*>(word), 0, sizeof(int), static_cast<cudaStream_t>(stream)));
   return 0;
 }
+
+#ifdef GA_TC_TRACE
+// Profiling builds only: copies the timeline the traced CTA of the tcgen05 kernel left behind to `host_dst`
+// (TC_TRACE_ROLES x TC_TRACE_CAP int64 words) and clears it.
+int ga_tc_trace_read(void* host_dst) {
+  constexpr size_t n = sizeof(long long) * ga::attn::tc::TC_TRACE_ROLES * ga::attn::tc::TC_TRACE_CAP;
+  GA_CUDA(cudaDeviceSynchronize());
+  GA_CUDA(cudaMemcpyFromSymbol(host_dst, ga::attn::tc::g_tc_trace, n));
+  void* dev = nullptr;
+  GA_CUDA(cudaGetSymbolAddress(&dev, ga::attn::tc::g_tc_trace));
+  GA_CUDA(cudaMemset(dev, 0, n));
+  return 0;
+}
+#endif
 
 }  // extern "C"

@@ -66,6 +66,9 @@ struct AttnDev {
   int box_tok;       // tokens per TMA box = min(page_size, TN)
   int max_q;         // decode/verify: query tokens per request are capped here (rows <= 16*MT)
   int bq;            // extend: query tokens per row block
+  int tc_mode;       // tcgen05 kernel: 0 = slices of the tile stream (decode / verify route), 1 = extend items
+  int nblk;          // tcgen05 extend: the host's upper bound on the number of query blocks
+  int rows_cap;      // rows per workspace slot (row stride of ws_o / ws_lse)
   // split-KV workspace
   int* status;
   int* prefix;       // [batch + 1] exclusive prefix of per-request tile counts (written by CTA 0)
@@ -89,7 +92,8 @@ __device__ __forceinline__ int seq_len_checked(const AttnDev& p, int b) {
   }
   return L;
 }
-__device__ __forceinline__ SeqInfo seq_info(const AttnDev& p, int b) {
+// `tile`: KV tokens per tile of the caller's stream (TN for the warp-level kernel, 128 for the tcgen05 one).
+__device__ __forceinline__ SeqInfo seq_info(const AttnDev& p, int b, int tile = TN) {
   SeqInfo s;
   s.L = seq_len_checked(p, b);
   int ql = p.cu[b + 1] - p.cu[b];
@@ -99,13 +103,13 @@ __device__ __forceinline__ SeqInfo seq_info(const AttnDev& p, int b) {
     s.cnt = 0;
     return s;
   }
-  int thi = (s.L + TN - 1) / TN;
+  int thi = (s.L + tile - 1) / tile;
   int lower = 0;
   if (p.window_left >= 0) {
     lower = s.L - s.ql - p.window_left;
     if (lower < 0) lower = 0;
   }
-  s.tlo = lower / TN;
+  s.tlo = lower / tile;
   s.cnt = thi - s.tlo;
   return s;
 }
@@ -135,15 +139,16 @@ struct Seg {
 struct SliceWalker {
   long long g0, g1, u0;
   int b, h, cnt, tlo, L, ql;
-  int cta;
+  int cta, tile;
   bool live;
 
-  __device__ void init(const AttnDev& p, int cta_, int G, int lane) {
+  __device__ void init(const AttnDev& p, int cta_, int G, int lane, int tile_ = TN) {
     cta = cta_;
+    tile = tile_;
     long long sum = 0;
     for (int b0 = 0; b0 < p.batch; b0 += 32) {
       int bb = b0 + lane;
-      sum += bb < p.batch ? seq_info(p, bb).cnt : 0;
+      sum += bb < p.batch ? seq_info(p, bb, tile).cnt : 0;
     }
 #pragma unroll
     for (int d = 16; d; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
@@ -156,7 +161,7 @@ struct SliceWalker {
     b = -1;
     for (int b0 = 0; b0 < p.batch && b < 0; b0 += 32) {
       int bb = b0 + lane;
-      int c = bb < p.batch ? seq_info(p, bb).cnt : 0;
+      int c = bb < p.batch ? seq_info(p, bb, tile).cnt : 0;
       int incl = warp_incl_scan(c, lane);
       unsigned hit = __ballot_sync(0xffffffffu, (pre + incl) * p.kvh > g0);
       if (hit) {
@@ -178,7 +183,7 @@ struct SliceWalker {
     u0 = pre * p.kvh + static_cast<long long>(h) * cnt;
   }
   __device__ void load(const AttnDev& p) {
-    SeqInfo s = seq_info(p, b);
+    SeqInfo s = seq_info(p, b, tile);
     cnt = s.cnt;
     tlo = s.tlo;
     L = s.L;
@@ -216,6 +221,19 @@ struct SliceWalker {
     return true;
   }
 };
+
+// One warp writes the exclusive prefix of the per-request tile counts the combine kernel works from.
+__device__ __forceinline__ void publish_prefix(const AttnDev& p, int lane, int tile) {
+  int pre = 0;
+  for (int b0 = 0; b0 < p.batch; b0 += 32) {
+    int bb = b0 + lane;
+    int c = bb < p.batch ? seq_info(p, bb, tile).cnt : 0;
+    int incl = warp_incl_scan(c, lane);
+    if (bb < p.batch) p.prefix[bb] = pre + incl - c;
+    pre += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) p.prefix[p.batch] = pre;
+}
 
 // Extend: row block `x` of the call (heaviest, i.e. latest, blocks first) for kv head `h`. Every warp runs an
 // identical copy. `tile` is the KV tile size the caller iterates in. Returns false when x is past the last block.
@@ -864,17 +882,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
   bool one_pending = false;
   if (MODE == 0) {
     walk.init(p, blockIdx.x, gridDim.x, lane);
-    if (blockIdx.x == 0 && warp == 0) {  // publish the per-request prefix for the combine kernel
-      int pre = 0;
-      for (int b0 = 0; b0 < p.batch; b0 += 32) {
-        int bb = b0 + lane;
-        int c = bb < p.batch ? seq_info(p, bb).cnt : 0;
-        int incl = warp_incl_scan(c, lane);
-        if (bb < p.batch) p.prefix[bb] = pre + incl - c;
-        pre += __shfl_sync(0xffffffffu, incl, 31);
-      }
-      if (lane == 0) p.prefix[p.batch] = pre;
-    }
+    if (blockIdx.x == 0 && warp == 0) publish_prefix(p, lane, TN);
   } else {
     one_pending = extend_block(p, static_cast<int>(blockIdx.x), static_cast<int>(blockIdx.y), TN, lane, one);
   }
@@ -1136,11 +1144,12 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
 // that a single CTA finished alone, and merges the partials of split units in slice order
 // (math of the reference's combine kernel, kernel.cuh:665-749; no atomics, so bit-reproducible).
 template <int HD>
-__global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant__ AttnDev p, int G, int rows_cap) {
+__global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant__ AttnDev p, int G, int rows_cap,
+                                                          int tile) {
   const int b = blockIdx.x, h = blockIdx.y;
   grid_dep_wait();    // the whole decode grid has finished and its partials are visible
   grid_dep_launch();  // the next kernel in the stream may start its own prologue
-  SeqInfo si = seq_info(p, b);
+  SeqInfo si = seq_info(p, b, tile);
   int ql_all = p.cu[b + 1] - p.cu[b];
   if (ql_all <= 0) return;
   const int q0 = p.cu[b];

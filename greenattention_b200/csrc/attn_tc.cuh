@@ -7,19 +7,21 @@
 // bottom-right causal mask and left window, online softmax in the log2 domain, P rounded to e4m3, O = v_descale
 // * P V / l, natural-log LSE (kernel.cuh:468-474,489-496,621-653).
 //
-// One CTA = 128 query rows (128 / GQA tokens x the GQA heads of one kv head) against the keys they can see,
-// 128 keys per iteration:
+// A CTA works on 128 query rows at a time (128 / GQA tokens x the GQA heads of one kv head) against the keys they
+// can see, 128 keys per iteration, and is persistent: it walks a list of such segments (see TcWork) with tensor
+// memory, barriers and pipelines set up once. 22 warps:
 //   * four producer warps (K / V x even / odd tiles) gather pages with TMA (128-byte swizzle, one box per page
 //     and 128-byte head slice, never multicast) into a K ring and a V ring;
-//   * one lane of the last warp issues the MMAs: S = Q K^T with both operands K-major straight from the swizzled
-//     tiles, and O += P V with P as a K-major A operand from shared memory and V as an MN-major B operand, i.e.
-//     the [token, dim] page layout as it is: no transpose of V anywhere. S (2 x 128 columns, double
-//     buffered) and O (head_dim columns) live in tensor memory;
-//   * warps 0-7 (softmax): two threads per query row (= tensor-memory lane), one per half of the 128 keys. Each reads its S half-row with
-//     tcgen05.ld, does mask / max / exp2 without any cross-thread traffic, writes P as two e4m3 terms
-//     (4 significant bits + residual, so a probability carries ~2^-8 relative error) into swizzled shared
-//     memory, and rescales O in tensor memory only when its running max moved by more than 1.5 in log2 (the
-//     stale max keeps P below the e4m3 limit: 2^(7 + 1.5) < 448).
+//   * two issuing lanes in two warps of their own: one issues S = Q K^T with both operands K-major straight from
+//     the swizzled tiles, the other O += P V with P as a K-major A operand from shared memory and V as an MN-major
+//     B operand, i.e. the [token, dim] page layout as it is: no transpose of V anywhere. S (2 or 3 buffers of 128
+//     columns) and O (head_dim columns) live in tensor memory;
+//   * 16 softmax warps in two groups that alternate over the key tiles, two threads per query row (= tensor-memory
+//     lane), one per half of the 128 keys. Each reads its S half-row with tcgen05.ld, exchanges the row maximum
+//     with its partner through shared memory, runs the exp2 pass and writes P as e4m3 (plus a residual term while
+//     a row rests on few keys, so that a probability carries ~2^-8 relative error) into swizzled shared memory,
+//     and rescales O in tensor memory only when the running max moved by more than 1.5 in log2 (the stale max
+//     keeps P below the e4m3 limit: 2^(7 + 1.5) < 448).
 // Every wait is bounded; a wait that runs out records a status word and the CTA drains to its common exit,
 // where tensor memory is released.
 #pragma once
@@ -121,7 +123,8 @@ struct TcCfg {
   // 256 this fills the 227 KiB of an SM exactly, so the kernel relies on the 1024-byte alignment it declares for
   // its dynamic shared memory and checks it at run time.
   static constexpr int BAR_OFF = 0;
-  static constexpr int X_OFF = 256;                   // part maxima [2][2][128] bf16, running max [2][128] f32; row sums overlay both
+  static constexpr int X_OFF = 512;                   // part maxima [2][2][128] bf16, running max [2][128] f32; row sums overlay both
+  static constexpr int SEG_OFF = X_OFF + 2048;        // ring of segment descriptors written by the scheduler warp
   static constexpr int Q_OFF = 3072;
   static constexpr int P_OFF = Q_OFF + Q_BYTES;       // [buffer 0|1][hi|lo]
   static constexpr int K_OFF = P_OFF + 4 * P_BYTES;
@@ -190,13 +193,106 @@ __device__ __forceinline__ float exp_chunk32(const uint32_t (&v)[N], float sl2, 
   return (l4[0] + l4[1]) + (l4[2] + l4[3]);
 }
 
-// Threads: 16 softmax warps (two groups of 8), 4 producer warps, 2 MMA-issuing warps.
+// Class of the 32 key columns starting at `col0` for the 32 rows of a warp (row of this lane: visible keys are
+// [lo_key, pos], pos = -1 for a padding row): 4 = no row sees any of them, 0 = every row sees all of them, else a
+// mixed chunk with bit 0 set when some row is cut by its upper bound (the causal diagonal) and bit 1 when some row
+// is cut by its lower bound (the window edge). Warp-uniform; all lanes call it together.
+__device__ __forceinline__ int chunk_class(int col0, int pos, int lo_key) {
+  if (__all_sync(0xffffffffu, col0 > pos || col0 + 31 < lo_key)) return 4;
+  const int hi = __all_sync(0xffffffffu, col0 + 31 <= pos) ? 0 : 1;
+  const int lo = __all_sync(0xffffffffu, col0 >= lo_key) ? 0 : 2;
+  return hi | lo;
+}
+// Masks a mixed chunk of raw scores in registers (hidden keys become -inf) and folds the visible ones into the
+// four partial maxima. HI / LO: which of the two bounds can cut a row of this warp here.
+template <bool HI, bool LO>
+__device__ __forceinline__ void mask_chunk32(uint32_t (&v)[32], int col0, int pos, int lo_key, float (&m4)[4]) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const int col = col0 + j;
+    const bool vis = (!HI || col <= pos) && (!LO || col >= lo_key);
+    const float x = vis ? __uint_as_float(v[j]) : -INFINITY;
+    v[j] = __float_as_uint(x);
+    m4[j & 3] = fmaxf(m4[j & 3], x);
+  }
+}
+
+// Optional timeline of one CTA (build with -DGA_TC_TRACE): a handful of threads, one per role, append
+// (event, tile, SM clock) words to a device array that a profiling script reads back. Compiles to nothing
+// in the product build.
+#ifdef GA_TC_TRACE
+constexpr int TC_TRACE_ROLES = 8, TC_TRACE_CAP = 8192;
+__device__ long long g_tc_trace[TC_TRACE_ROLES][TC_TRACE_CAP];
+#define TC_TRACE(kind, tile)                                                                                    \
+  do {                                                                                                          \
+    if (trc != nullptr && trc_n < TC_TRACE_CAP)                                                                 \
+      trc[trc_n++] = (static_cast<long long>(((kind) << 16) | ((tile) & 0xffff)) << 40) | (clock64() & 0xffffffffffll); \
+  } while (0)
+#else
+#define TC_TRACE(kind, tile)
+#endif
+
+// Threads: 16 softmax warps (two groups of 8), 4 producer warps, 2 MMA-issuing warps, 1 scheduler warp.
 constexpr int TC_SOFTMAX = 512;
 constexpr int TC_GROUP = 256;
-constexpr int TC_THREADS = TC_SOFTMAX + 192;
+constexpr int TC_THREADS = TC_SOFTMAX + 224;
+constexpr int SEGQ = 8;          // depth of the segment ring
+constexpr int SEG_WORDS = 10;    // b, h, q0, nq, pos0, L, t_lo, t_hi, slot, valid
+constexpr int SEG_READERS = 22;  // warps that consume every segment: 16 softmax, 4 producers, 2 issuing
+
+// Work source of a persistent CTA, run by its scheduler warp (all 32 lanes call next()).
+//   mode 0 (decode / verify route): the call is one stream of 128-key tiles ordered by (request, kv head) and CTA c
+//     takes the contiguous slice [c T / G, (c + 1) T / G) of it, exactly as the warp-level decode kernel does, so
+//     any batch and any mix of lengths balances to one tile; a unit that a slice cuts is finished by the combine
+//     kernel from the partial (O, LSE) the CTAs leave in the workspace slots.
+//   mode 1 (extend): items are (query block, kv head) pairs, latest (heaviest) blocks first; item i is block
+//     i % nblk of kv head i / nblk, where nblk is the host's upper bound on the number of blocks (items past the
+//     real count are skipped). CTAs claim items one at a time from a counter in the workspace header, so SMs that
+//     drew lighter items take more of them; the last CTA to finish puts the counters back to zero for the next call.
+struct TcWork {
+  SliceWalker walk;
+  int mode, item_end, nblk;
+  int* counters;  // [0] next item, [1] CTAs that have finished claiming
+  __device__ void init(const AttnDev& p, int lane) {
+    mode = p.tc_mode;
+    nblk = p.nblk;
+    item_end = p.nblk * p.kvh;
+    counters = p.status + 1;
+    if (mode == 0) walk.init(p, blockIdx.x, gridDim.x, lane, TNK);
+  }
+  __device__ bool next(const AttnDev& p, int lane, Seg& s) {
+    if (mode == 0) return walk.next(p, s);
+    while (true) {
+      int i = 0;
+      if (lane == 0) i = atomicAdd(counters, 1);
+      i = __shfl_sync(0xffffffffu, i, 0);
+      if (i >= item_end) return false;
+      const int h = i / nblk;
+      if (extend_block(p, i - h * nblk, h, TNK, lane, s)) return true;
+    }
+  }
+  // Called once by every CTA after its last claim.
+  __device__ void finish(int lane) {
+    if (mode == 1 && lane == 0) {
+      __threadfence();
+      if (atomicAdd(counters + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+        atomicExch(counters, 0);
+        atomicExch(counters + 1, 0);
+      }
+    }
+  }
+};
 
 // REP: instance for calls with at most 32 rows per kv head (see the softmax section); extend uses REP = false so
 // that its inner loops carry none of that mode's branches.
+//
+// The CTA is persistent: tensor memory, barriers and the zeroed parts of shared memory are set up once and the
+// CTA then walks its segments (TcWork). Ring stages, score buffers, P buffers and the running-max chain are
+// indexed by the CTA's running tile count `it`, so the producers, the two issuing lanes and the softmax groups
+// run on across segment boundaries: the K/V tiles of the next segment are in flight while the current one is
+// in its last tiles and its epilogue. Two more barriers order what a segment boundary shares: `qfree` (the last
+// QK MMA of a segment has read the Q tile, committed by the QK lane) before the softmax warps overwrite Q, and
+// `ofree` (every softmax thread has read O out of tensor memory) before the PV lane starts a new accumulation.
 template <int HD, bool REP>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
@@ -217,15 +313,26 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
                  b_mpub = bars + 88;
   const uint32_t b_kfull = bars + 104, b_kempty = b_kfull + 8 * C::NKV, b_vfull = b_kempty + 8 * C::NKV,
                  b_vempty = b_vfull + 8 * C::NKV;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 104 + 32 * C::NKV);
+  const uint32_t b_qfree = b_vempty + 8 * C::NKV, b_ofree = b_qfree + 8;
+  const uint32_t b_segfull = b_ofree + 8, b_segfree = b_segfull + 8 * SEGQ;
+  const int* segq = reinterpret_cast<const int*>(gen + C::SEG_OFF);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 104 + 32 * C::NKV + 16 + 16 * SEGQ);
   uint32_t* lo_flag = tmem_slot + 2;  // [group][2]: the residual term of P is wanted for the group's tile 2u + g
   __nv_bfloat16* mxbuf = reinterpret_cast<__nv_bfloat16*>(gen + C::X_OFF);  // [group][part][128], rounded up
   float* mrun = reinterpret_cast<float*>(gen + C::X_OFF + 1024);            // [group][128] running max after a tile
   float* lbuf = reinterpret_cast<float*>(gen + C::X_OFF);  // [4][128] row sums, after the last tile (overlay)
+  static_assert(104 + 32 * C::NKV + 16 + 16 * SEGQ + 8 + 16 <= C::X_OFF, "barrier block overruns the exchange buffers");
+  static_assert(C::SEG_OFF + SEGQ * SEG_WORDS * 4 <= C::Q_OFF, "segment ring overruns the Q tile");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     mbar_init(b_q, TC_SOFTMAX);
+    mbar_init(b_qfree, 1);
+    mbar_init(b_ofree, TC_SOFTMAX);
+    for (int i = 0; i < SEGQ; ++i) {
+      mbar_init(b_segfull + 8 * i, 1);
+      mbar_init(b_segfree + 8 * i, SEG_READERS);
+    }
     for (int i = 0; i < 2; ++i) {
       mbar_init(b_pready + 8 * i, TC_GROUP);
       mbar_init(b_pfree + 8 * i, 1);
@@ -241,9 +348,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       mbar_init(b_vfull + 8 * i, 1);
       mbar_init(b_vempty + 8 * i, 1);
     }
-    // the first tile of each group always carries the residual term; later tiles by vote
-    lo_flag[0] = lo_flag[2] = 1u;
-    lo_flag[1] = lo_flag[3] = 0u;
+    lo_flag[0] = lo_flag[1] = lo_flag[2] = lo_flag[3] = 0u;
     mbar_fence_init();
   }
   if (warp == 0) {
@@ -257,12 +362,39 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  Seg s;
-  const bool have = extend_block(p, static_cast<int>(blockIdx.x), static_cast<int>(blockIdx.y), TNK, lane, s);
-  const int n_tiles = have ? s.t_hi - s.t_lo : 0;
   bool failed = false;
+  int it = 0;  // tiles of this CTA so far: position in every ring, shared by all roles
+  int sq = 0;  // segments with at least one tile so far: phase of the Q / O hand-over barriers
+  int sk = 0;  // segments read from the scheduler's ring so far
+#ifdef GA_TC_TRACE
+  long long* trc = nullptr;
+  int trc_n = 0;
+  if (blockIdx.x == 3) {
+    const int role = tid == 0 ? 0 : tid == 256 ? 1 : tid == 640 ? 2 : tid == 672 ? 3 : tid == 512 ? 4 : tid == 544 ? 5 : -1;
+    if (role >= 0) trc = g_tc_trace[role];
+  }
+#endif
+  // Segment `k` of this CTA from the scheduler's ring (all lanes of a consumer warp call this together). With
+  // `release` the warp hands the ring slot back; a peek at the next segment leaves it in place. False at the end
+  // of the list or after a wait ran out anywhere in the warp.
+  auto read_seg = [&](int k, Seg& s, bool release) -> bool {
+    const int slot = k % SEGQ;
+    wait_or_flag(b_segfull + 8 * slot, (k / SEGQ) & 1, failed, p.status, GA_ST_WAIT_FULL);
+    TC_TRACE(17, k);
+    failed = __any_sync(0xffffffffu, failed);
+    if (failed) return false;
+    const int* q = segq + slot * SEG_WORDS;
+    s.b = q[0], s.h = q[1], s.q0 = q[2], s.nq = q[3], s.pos0 = q[4], s.L = q[5], s.t_lo = q[6], s.t_hi = q[7], s.slot = q[8];
+    const bool valid = q[9] != 0;
+    if (release) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(b_segfree + 8 * slot);
+    }
+    return valid;
+  };
+  Seg cur;
 
-  if (have && warp >= 16 && warp < 20) {
+  if (warp >= 16 && warp < 20) {
     // ---------------------------------------------------------------- producers: four warps
     // One warp's issue loop (barrier wait, expect_tx, page lookup, TMA issue) takes more than a thousand cycles
     // per tile, so K and V have their own warps, and even and odd tiles too. The ring depth is even, so a stage
@@ -273,90 +405,160 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     win.base = win.cur = win.nxt = 0;
     if (lane == 0) tma_prefetch_desc(kv ? &vmap : &kmap);
     const int nbox = TNK / p.box_tok;
-    for (int t = par; t < n_tiles; t += 2) {
-      const int st = t % C::NKV, use = t / C::NKV;
-      const int n0 = (s.t_lo + t) * TNK;
-      int boxes = 0;
-      for (int i = 0; i < nbox; ++i) boxes += (n0 + i * p.box_tok) < s.L;
-      const uint32_t bytes = static_cast<uint32_t>(boxes) * p.box_tok * 128 * C::ATOMS;
-      const uint32_t full = (kv ? b_vfull : b_kfull) + 8 * st, empty = (kv ? b_vempty : b_kempty) + 8 * st;
-      if (use > 0) wait_or_flag(empty, (use - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
-      if (failed) break;
-      if (lane == 0) mbar_expect_tx(full, bytes);
-      __syncwarp();
-      for (int i = 0; i < boxes; ++i) {
-        const int n = n0 + i * p.box_tok;
-        int page = pt_lookup(p, win, s.b, n >> p.page_shift, lane);
-        if ((page < 0 || page >= p.num_pages) && lane == 0) atomicExch(p.status, GA_ST_BAD_PAGE);
-        if (lane < C::ATOMS) {
-          const uint32_t dst = (kv ? sV : sK) + st * C::KV_BYTES + lane * SLAB + i * p.box_tok * 128;
-          tma_load_4d(dst, kv ? &vmap : &kmap, full, lane * 128, s.h, n & p.page_mask, page);
+    while (read_seg(sk++, cur, true)) {
+      const Seg& s = cur;
+      const int n_tiles = s.t_hi - s.t_lo;
+      for (int t = 0; t < n_tiles && !failed; ++t, ++it) {
+        if ((it & 1) != par) continue;
+        const int st = it % C::NKV, use = it / C::NKV;
+        const int n0 = (s.t_lo + t) * TNK;
+        int boxes = 0;
+        for (int i = 0; i < nbox; ++i) boxes += (n0 + i * p.box_tok) < s.L;
+        const uint32_t bytes = static_cast<uint32_t>(boxes) * p.box_tok * 128 * C::ATOMS;
+        const uint32_t full = (kv ? b_vfull : b_kfull) + 8 * st, empty = (kv ? b_vempty : b_kempty) + 8 * st;
+        if (use > 0) wait_or_flag(empty, (use - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        if (failed) break;
+        TC_TRACE(40, it);
+        if (lane == 0) mbar_expect_tx(full, bytes);
+        __syncwarp();
+        for (int i = 0; i < boxes; ++i) {
+          const int n = n0 + i * p.box_tok;
+          int page = pt_lookup(p, win, s.b, n >> p.page_shift, lane);
+          if ((page < 0 || page >= p.num_pages) && lane == 0) atomicExch(p.status, GA_ST_BAD_PAGE);
+          if (lane < C::ATOMS) {
+            const uint32_t dst = (kv ? sV : sK) + st * C::KV_BYTES + lane * SLAB + i * p.box_tok * 128;
+            tma_load_4d(dst, kv ? &vmap : &kmap, full, lane * 128, s.h, n & p.page_mask, page);
+          }
         }
+        TC_TRACE(41, it);
       }
     }
-  } else if (have && warp == 20) {
+  } else if (warp == 20) {
     // ---------------------------------------------------------------- QK issue: one lane
     // The two issuing lanes (this one and the PV one) run on their own: the next scores are what a softmax group
     // waits for once it hands back its S buffer, so they must not queue behind the PV wait. Each lane's
     // instruction stream is the limit of the tensor pipe here, so descriptors are whole 64-bit registers
     // prepared before the waits, and a K step is one add.
-    if (lane == 0) {
-      const uint32_t id_qk = instr_desc(TM, TNK, 0);
-      const uint64_t dq = smem_desc(sQ, 16, 1024), dk = smem_desc(sK, 16, 1024);
-      wait_or_flag(b_q, 0, failed, p.status, GA_ST_WAIT_FULL);
-      for (int t = 0; t < n_tiles && !failed; ++t) {
-        const int st = t % C::NKV;
-        const uint64_t kb = dk + static_cast<uint64_t>(st * (C::KV_BYTES >> 4));
-        const int sb = t % C::NS;
-        const uint32_t sd = tmem + C::S_COL + sb * 128;
-        wait_or_flag(b_kfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
-        if (t >= C::NS) wait_or_flag(b_sfree + 8 * sb, ((t / C::NS) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
-        if (failed) break;
-        tc_fence_after();
+    const uint32_t id_qk = instr_desc(TM, TNK, 0);
+    const uint64_t dq = smem_desc(sQ, 16, 1024), dk = smem_desc(sK, 16, 1024);
+    while (read_seg(sk++, cur, true)) {
+      const int n_tiles = cur.t_hi - cur.t_lo;
+      if (lane == 0 && n_tiles > 0 && !failed) {
+        wait_or_flag(b_q, sq & 1, failed, p.status, GA_ST_WAIT_FULL);  // this segment's Q tile is in place
+        TC_TRACE(20, it);
+        for (int t = 0; t < n_tiles && !failed; ++t, ++it) {
+          const int st = it % C::NKV;
+          const uint64_t kb = dk + static_cast<uint64_t>(st * (C::KV_BYTES >> 4));
+          const int sb = it % C::NS;
+          const uint32_t sd = tmem + C::S_COL + sb * 128;
+          wait_or_flag(b_kfull + 8 * st, (it / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
+          TC_TRACE(21, it);
+          if (it >= C::NS) wait_or_flag(b_sfree + 8 * sb, ((it / C::NS) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+          if (failed) break;
+          TC_TRACE(22, it);
+          tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < HD / 32; ++ks) {
-          const uint64_t off = static_cast<uint64_t>(((ks >> 2) * SLAB + (ks & 3) * 32) >> 4);
-          mma_f8(sd, dq + off, kb + off, id_qk, ks > 0 ? 1 : 0);
+          for (int ks = 0; ks < HD / 32; ++ks) {
+            const uint64_t off = static_cast<uint64_t>(((ks >> 2) * SLAB + (ks & 3) * 32) >> 4);
+            mma_f8(sd, dq + off, kb + off, id_qk, ks > 0 ? 1 : 0);
+          }
+          mma_commit(b_kempty + 8 * st);
+          mma_commit(b_sfull + 8 * sb);
+          TC_TRACE(23, it);
         }
-        mma_commit(b_kempty + 8 * st);
-        mma_commit(b_sfull + 8 * sb);
+        if (!failed) mma_commit(b_qfree);  // every QK MMA of the segment has read Q
       }
+      if (n_tiles > 0) ++sq;
+      __syncwarp();
     }
-  } else if (have && warp == 21) {
+  } else if (warp == 21) {
     // ---------------------------------------------------------------- PV issue: one lane
     // O += P V with V as an MN-major B operand covering all head dims in one instruction (N = head_dim: at 256
     // the second 128-dim slab is found through the leading-dimension stride of the descriptor).
-    if (lane == 0) {
-      const uint32_t id_pv = instr_desc(TM, HD, 1);
-      const uint64_t dp = smem_desc(sP, 16, 1024), dv = smem_desc(sV, SLAB, 1024);
-      for (int t = 0; t < n_tiles && !failed; ++t) {
-        const int st = t % C::NKV;
-        const uint64_t vb = dv + static_cast<uint64_t>(st * (C::KV_BYTES >> 4));
-        const uint64_t pb = dp + static_cast<uint64_t>((t & 1) * 2 * (C::P_BYTES >> 4));
-        wait_or_flag(b_pready + 8 * (t & 1), (t >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
-        wait_or_flag(b_vfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
-        if (failed) break;
-        tc_fence_after();
-        const int terms = atomicExch(lo_flag + (t & 1) * 2 + ((t >> 1) & 1), 0u) ? 2 : 1;
+    const uint32_t id_pv = instr_desc(TM, HD, 1);
+    const uint64_t dp = smem_desc(sP, 16, 1024), dv = smem_desc(sV, SLAB, 1024);
+    while (read_seg(sk++, cur, true)) {
+      const int n_tiles = cur.t_hi - cur.t_lo;
+      if (lane == 0 && n_tiles > 0 && !failed) {
+        // the first PV MMA of a segment overwrites O: the epilogue of the segment before must have read it
+        if (sq > 0) wait_or_flag(b_ofree, (sq - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        TC_TRACE(30, it);
+        for (int t = 0; t < n_tiles && !failed; ++t, ++it) {
+          const int st = it % C::NKV, g = it & 1;
+          const uint64_t vb = dv + static_cast<uint64_t>(st * (C::KV_BYTES >> 4));
+          const uint64_t pb = dp + static_cast<uint64_t>(g * 2 * (C::P_BYTES >> 4));
+          wait_or_flag(b_pready + 8 * g, (it >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
+          TC_TRACE(31, it);
+          wait_or_flag(b_vfull + 8 * st, (it / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
+          if (failed) break;
+          TC_TRACE(32, it);
+          tc_fence_after();
+          // residual term: always on the first tile of each group in a segment, later by the softmax threads' vote
+          const bool voted = atomicExch(lo_flag + g * 2 + ((it >> 1) & 1), 0u) != 0u;
+          const int terms = (voted || t < 2) ? 2 : 1;
 #pragma unroll 1
-        for (int term = 0; term < terms; ++term) {  // hi term, then the residual term while some row needs it
-          const uint64_t pa = pb + static_cast<uint64_t>(term * (C::P_BYTES >> 4));
+          for (int term = 0; term < terms; ++term) {  // hi term, then the residual term while some row needs it
+            const uint64_t pa = pb + static_cast<uint64_t>(term * (C::P_BYTES >> 4));
 #pragma unroll
-          for (int ks = 0; ks < TNK / 32; ++ks)
-            mma_f8(tmem + C::O_COL, pa + static_cast<uint64_t>(ks * 2), vb + static_cast<uint64_t>(ks * (32 * 128 >> 4)), id_pv,
-                   (t > 0 || term > 0 || ks > 0) ? 1 : 0);
+            for (int ks = 0; ks < TNK / 32; ++ks)
+              mma_f8(tmem + C::O_COL, pa + static_cast<uint64_t>(ks * 2), vb + static_cast<uint64_t>(ks * (32 * 128 >> 4)), id_pv,
+                     (t > 0 || term > 0 || ks > 0) ? 1 : 0);
+          }
+          mma_commit(b_vempty + 8 * st);
+          mma_commit(b_pfree + 8 * g);
+          TC_TRACE(33 + (terms - 1), it);
         }
-        mma_commit(b_vempty + 8 * st);
-        mma_commit(b_pfree + 8 * (t & 1));
       }
+      if (n_tiles > 0) ++sq;
+      __syncwarp();
     }
-  } else if (have && warp < 16) {
+  } else if (warp == 22) {
+    // ---------------------------------------------------------------- scheduler: one warp
+    // Derives this CTA's segments (device split plan / item list, with the global reads that takes) a ring's depth
+    // ahead of the warps that consume them, so neither those reads nor the walker's state sit in the other roles.
+    TcWork work;
+    work.init(p, lane);
+    if (p.tc_mode == 0 && blockIdx.x == 0) publish_prefix(p, lane, TNK);  // for the combine kernel
+    int* wq = reinterpret_cast<int*>(gen + C::SEG_OFF);
+    for (int k = 0;; ++k) {
+      const int slot = k % SEGQ;
+      if (k >= SEGQ) wait_or_flag(b_segfree + 8 * slot, ((k / SEGQ) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      // extend items are claimed from a counter all CTAs share: take the next one only when every warp has picked
+      // up the one before, so a CTA never sits on more than one item it has not started
+      if (p.tc_mode == 1 && k >= 1)
+        wait_or_flag(b_segfree + 8 * ((k - 1) % SEGQ), ((k - 1) / SEGQ) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      failed = __any_sync(0xffffffffu, failed);
+      if (failed) break;
+      Seg s;
+      const bool more = work.next(p, lane, s);
+      if (more && s.t_hi > s.t_lo) {
+        // the segment's query rows, pulled into the L2 now: the softmax warps load them one segment from here
+        const int esz = p.q_bf16 ? 2 : 1, lines = (HD * esz + 127) / 128, rows = s.nq * p.gqa;
+        for (int i = lane; i < rows * lines; i += 32) {
+          const int row = i / lines, ln = i - row * lines;
+          const int tq = row / p.gqa, hq = row - tq * p.gqa;
+          const uint8_t* a = p.q + (static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1) * esz + ln * 128;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+        }
+      }
+      if (lane == 0) {
+        int* q = wq + slot * SEG_WORDS;
+        q[0] = s.b, q[1] = s.h, q[2] = s.q0, q[3] = s.nq, q[4] = s.pos0, q[5] = s.L, q[6] = s.t_lo, q[7] = s.t_hi, q[8] = s.slot;
+        q[9] = more ? 1 : 0;
+        mbar_arrive(b_segfull + 8 * slot);  // release: the words above are visible to whoever sees the phase
+      }
+      __syncwarp();
+      if (!more) break;
+    }
+    work.finish(lane);
+  } else if (warp < 16) {
     // ---------------------------------------------------------------- softmax: two groups of 256 threads
-    // Group g takes the tiles of parity g (its own S and P buffers), two threads per query row: thread (r, hf) owns
-    // row r = tensor-memory lane, key columns [64 hf, 64 hf + 64) of the tile and the matching part of the output
-    // dims. While one group is in its exp2 pass (the SM's 16 exp2 per clock are the floor of a tile), the other
-    // waits for scores, reads them and finds its row maxima. The running max is one chain over all tiles: a group
-    // takes the value the other group published for the tile before, decides, and publishes its own.
+    // Group g takes the tiles of parity g of the CTA's running tile count (its own S and P buffers), two threads per
+    // query row: thread (r, hf) owns row r = tensor-memory lane, key columns [64 hf, 64 hf + 64) of the tile and the
+    // matching part of the output dims. While one group is in its exp2 pass (the SM's 16 exp2 per clock are the
+    // floor of a tile), the other waits for scores, reads them and finds its row maxima. The running max is one
+    // chain over the tiles of a segment: a group takes the value the other group published for the tile before,
+    // decides, and publishes its own.
     //
     // Few rows (speculative verify: query tokens x GQA <= 32): the rows are replicated into all four 32-lane
     // quarters of the Q tile, so S comes out four times and each quarter's warps take a quarter of the key
@@ -365,255 +567,404 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     // one scheduler's exp2 unit. P rows 32..127 are zeroed once; O rows 0..31 are the result.
     const int g = tid >> 8, hf = (tid >> 7) & 1, r = tid & 127;
     const int part = g * 2 + hf;  // quarter of the head dims this thread loads of Q and stores of O
-    const bool rep = REP && s.nq * p.gqa <= 32;
+    constexpr bool rep = REP;
     const int qt = warp & 3;             // lane quarter of this warp
     const int rr = rep ? (r & 31) : r;   // the query row this thread works for
-    const int tq = rr / p.gqa, hq = rr - tq * p.gqa;
-    const bool valid = tq < s.nq;
-    const bool warp_live = rep || qt * 32 < s.nq * p.gqa;  // some row of this warp is a real query row
-    const bool owns_o = !rep || qt == 0;                   // this warp's lanes of O are result rows
+    const bool owns_o = !rep || qt == 0; // this warp's lanes of O are result rows
     const int col_first = rep ? 32 * qt + 16 * hf : hf * CW;  // first key column of this thread's share of a tile
-    const int pos = valid ? s.pos0 + tq : -1;
-    const int lo_key = p.window_left >= 0 ? pos - p.window_left : -(1 << 30);
-    {  // Q: a quarter of this row, rounded to e4m3, into the swizzled A tile
-      const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1;
-#pragma unroll 1
-      for (int c = part * (HD / 64); c < (part + 1) * (HD / 64); ++c) {
-        uint4 pk = make_uint4(0, 0, 0, 0);
-        if (valid) {
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t grp_bar = 2 + g;      // named barrier of this group
+    if (rep) {  // P rows 32..127 are never written in this mode and must read as zero
+      for (int i = tid; i < 4 * C::P_BYTES / 16; i += TC_SOFTMAX)
+        asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(sP + i * 16), "r"(0) : "memory");
+      fence_proxy_async();
+      named_bar_sync(1, TC_SOFTMAX);  // every zero is in place before any thread writes a P row
+    }
+    // Q of segment `s`: a quarter of this thread's row, rounded to e4m3, into the swizzled A tile; then the
+    // arrival that lets the QK lane start the segment.
+    auto load_q = [&](const Seg& s) {
+      // 16-element chunks of the 128 x HD tile are dealt to the 512 threads so that the lanes of a warp read whole
+      // rows (32 contiguous bytes per lane, 2 or 4 rows per warp) instead of one 32-byte piece from each of 32 rows.
+      constexpr int NC = HD / 64;   // chunks per thread
+      constexpr int CPR = HD / 16;  // chunks per row
+      uint4 x[NC], y[NC];           // all global loads are issued before the first conversion
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int id = i * TC_SOFTMAX + tid, row = id / CPR, c = id - row * CPR;
+        const int qrow = rep ? (row & 31) : row;
+        const int tq = qrow / p.gqa, hq = qrow - tq * p.gqa;
+        x[i] = y[i] = make_uint4(0, 0, 0, 0);
+        if (tq < s.nq) {
+          const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1 + c * 16;
           if (p.q_bf16) {
-            const uint4* src = reinterpret_cast<const uint4*>(p.q + (off + c * 16) * 2);
-            uint4 x = src[0], y = src[1];
-            auto cv = [](uint32_t a, uint32_t b) {
-              return pack_e4m3x4(bf16_bits_to_f32(a & 0xffffu), bf16_bits_to_f32(a >> 16), bf16_bits_to_f32(b & 0xffffu),
-                                 bf16_bits_to_f32(b >> 16));
-            };
-            pk = make_uint4(cv(x.x, x.y), cv(x.z, x.w), cv(y.x, y.y), cv(y.z, y.w));
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + off * 2);
+            x[i] = src[0];
+            y[i] = src[1];
           } else {
-            pk = *reinterpret_cast<const uint4*>(p.q + off + c * 16);
+            x[i] = *reinterpret_cast<const uint4*>(p.q + off);
           }
         }
-        const uint32_t dst = sQ + (c >> 3) * SLAB + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+      }
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int id = i * TC_SOFTMAX + tid, row = id / CPR, c = id - row * CPR;
+        uint4 pk = x[i];
+        if (p.q_bf16) {
+          auto cv = [](uint32_t a, uint32_t b) {
+            return pack_e4m3x4(bf16_bits_to_f32(a & 0xffffu), bf16_bits_to_f32(a >> 16), bf16_bits_to_f32(b & 0xffffu),
+                               bf16_bits_to_f32(b >> 16));
+          };
+          pk = make_uint4(cv(x[i].x, x[i].y), cv(x[i].z, x[i].w), cv(y[i].x, y[i].y), cv(y[i].z, y[i].w));
+        }
+        const uint32_t dst = sQ + (c >> 3) * SLAB + row * 128 + (((c & 7) ^ (row & 7)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
                      : "memory");
       }
-      if (rep) {  // P rows 32..127 are never written in this mode and must read as zero
-        for (int i = tid; i < 4 * C::P_BYTES / 16; i += TC_SOFTMAX)
-          asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(sP + i * 16), "r"(0) : "memory");
-      }
+      TC_TRACE(18, 0);
       fence_proxy_async();
       mbar_arrive(b_q);
-      if (rep) named_bar_sync(1, TC_SOFTMAX);  // every zero is in place before any thread writes a P row
-    }
-    const float kds = p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f;
-    const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
-    const float sl2 = p.scale_log2 * kds;
-    const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const uint32_t grp_bar = 2 + g;        // named barrier of this group
-    float m_seen = -INFINITY, l = 0.f;     // l is relative to m_seen
-    for (int t = g; t < n_tiles; t += 2) {
-      const int u = t >> 1;                // this group's iteration: phases of its own barriers
-      const int n0 = (s.t_lo + t) * TNK;
-      const int c_base = n0 + col_first;
-      const bool need_mask = (n0 + TNK > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
-      const int sb = t % C::NS;            // score buffer of this tile
-      wait_or_flag(b_sfull + 8 * sb, (t / C::NS) & 1, failed, p.status, GA_ST_WAIT_FULL);
-      tc_fence_after();
-      const uint32_t s_addr = lane_base + C::S_COL + sb * 128 + col_first;
-      // pass 1: row max of the masked, scaled scores, 32 columns at a time (the scores stay in tensor memory)
-      float mx = -INFINITY;
-      if (warp_live) {
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (rep) {
-          uint32_t v[16];
-          tmem_ld16(s_addr, v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int col = c_base + j;
-            const float x = (!need_mask || (col <= pos && col >= lo_key)) ? __uint_as_float(v[j]) : -INFINITY;
-            m4[j & 3] = fmaxf(m4[j & 3], x);
-          }
+    };
+    bool q_ready = false;  // the Q tile of `cur` was already loaded during the segment before
+    while (read_seg(sk++, cur, true)) {
+      const Seg& s = cur;
+      const int n_tiles = s.t_hi - s.t_lo;
+      TC_TRACE(1, n_tiles);
+      // What only the end of the segment needs (output offsets, the value scale) is worked out there, so that it
+      // does not sit in registers through the tile loop.
+      const bool valid = rr / p.gqa < s.nq;
+      const bool warp_live = rep || qt * 32 < s.nq * p.gqa;  // some row of this warp is a real query row
+      if (n_tiles <= 0) {
+        // nothing visible (an empty cache or a window past the end): zero rows, -inf LSE; no barrier is touched
+        if (valid && owns_o) {
+          const int tq = rr / p.gqa, hq = rr - tq * p.gqa;
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(s.q0 + tq) * p.o_s0 +
+                               static_cast<long long>(s.h * p.gqa + hq) * p.o_s1 + part * (HD / 4);
+          for (int c0 = 0; c0 < HD / 4; c0 += 8) *reinterpret_cast<uint4*>(dst + c0) = make_uint4(0, 0, 0, 0);
+          if (part == 0 && p.lse != nullptr)
+            p.lse[static_cast<long long>(s.h * p.gqa + hq) * p.total_q + s.q0 + tq] = -INFINITY;
         }
-#pragma unroll 1
-        for (int c0 = 0; c0 < (rep ? 0 : CW); c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(s_addr + c0, v);
-          tmem_wait_ld();
-          if (need_mask) {
+        continue;
+      }
+      if (!q_ready) {
+        if (sq > 0) wait_or_flag(b_qfree, (sq - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        load_q(s);
+      }
+      TC_TRACE(2, it);
+      q_ready = false;
+      const int pos = valid ? s.pos0 + rr / p.gqa : -1;
+      const int lo_key = p.window_left >= 0 ? pos - p.window_left : -(1 << 30);
+      const float sl2 = p.scale_log2 * (p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f);
+      float m_seen = -INFINITY, l = 0.f;     // l is relative to m_seen
+      const int it0 = it;
+      for (int t = (g - it0) & 1; t < n_tiles; t += 2) {
+        const int gi = it0 + t;              // running tile index: buffers and barrier phases
+        const int u = gi >> 1;               // this group's iteration
+        const int n0 = (s.t_lo + t) * TNK;
+        const int c_base = n0 + col_first;
+        const bool need_mask = (n0 + TNK > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
+        const int sb = gi % C::NS;           // score buffer of this tile
+        TC_TRACE(3, gi);
+        wait_or_flag(b_sfull + 8 * sb, (gi / C::NS) & 1, failed, p.status, GA_ST_WAIT_FULL);
+        TC_TRACE(4, gi);
+        tc_fence_after();
+        const uint32_t s_addr = lane_base + C::S_COL + sb * 128 + col_first;
+        // pass 1: row max of the masked, scaled scores, 32 columns at a time (the scores stay in tensor memory)
+        float mx = -INFINITY;
+        if (warp_live) {
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          if (rep) {
+            uint32_t v[16];
+            tmem_ld16(s_addr, v);
+            tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = c_base + c0 + j;
-              const float x = (col <= pos && col >= lo_key) ? __uint_as_float(v[j]) : -INFINITY;
+            for (int j = 0; j < 16; ++j) {
+              const int col = c_base + j;
+              const float x = (!need_mask || (col <= pos && col >= lo_key)) ? __uint_as_float(v[j]) : -INFINITY;
               m4[j & 3] = fmaxf(m4[j & 3], x);
             }
-          } else {
+          }
+#pragma unroll 1
+          for (int c0 = 0; c0 < (rep ? 0 : CW); c0 += 32) {
+            // A 32-column chunk is classed for the whole warp: nothing visible (skipped), everything visible (the
+            // bare loop) or mixed (compares per element). On a diagonal or window-edge tile most chunks of a warp's
+            // 32 rows fall in the first two classes.
+            const int cls = need_mask ? chunk_class(c_base + c0, pos, lo_key) : 0;
+            if (cls == 4) continue;
+            uint32_t v[32];
+            tmem_ld32(s_addr + c0, v);
+            tmem_wait_ld();
+            if (cls != 0) {
+              // The masked scores go back into tensor memory, so the exp2 pass below reads every chunk the same
+              // way and needs no masked variant of its own.
+              if (cls == 1) mask_chunk32<true, false>(v, c_base + c0, pos, lo_key, m4);
+              else if (cls == 2) mask_chunk32<false, true>(v, c_base + c0, pos, lo_key, m4);
+              else mask_chunk32<true, true>(v, c_base + c0, pos, lo_key, m4);
+              tmem_st32(s_addr + c0, v);
+              tmem_wait_st();
+            } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
+              for (int j = 0; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
+            }
+          }
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * sl2;  // sl2 > 0; -inf stays -inf
+        }
+        // both parts publish their maximum rounded UP to bf16 and take the larger (a slightly high running max
+        // only makes P a little smaller)
+        TC_TRACE(5, gi);
+        mxbuf[(g * 2 + hf) * 128 + r] = __float2bfloat16_ru(mx);
+        // What does not depend on the partner's maximum is fetched before the exchange barrier, so that these
+        // round trips overlap the wait for the slowest warp of the group: the running max after the tile before
+        // from the other group, and the P buffer of this group (free once the PV MMAs of this group's previous
+        // tile are done; the residual flag of this tile is complete by then, every vote having preceded its
+        // thread's arrival for that tile). The waits follow the running tile count, also across a segment
+        // boundary, so every barrier is waited on once per phase.
+        float m_prev = -INFINITY;
+        if (gi >= 1) {
+          wait_or_flag(b_mpub + 8 * (g ^ 1), ((gi - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
+          if (t >= 1) m_prev = mrun[(g ^ 1) * 128 + r];
+        }
+        if (gi >= 2) wait_or_flag(b_pfree + 8 * g, (u - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        const bool with_lo = t < 2 || lo_flag[g * 2 + (u & 1)] != 0u;
+        TC_TRACE(6, gi);
+        named_bar_sync(grp_bar, TC_GROUP);
+        TC_TRACE(7, gi);
+        if (rep) {  // eight shares of a row: two parts in each of the four quarters
+          mx = -INFINITY;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4)
+            mx = fmaxf(mx, fmaxf(__bfloat162float(mxbuf[(g * 2) * 128 + rr + 32 * q4]),
+                                 __bfloat162float(mxbuf[(g * 2 + 1) * 128 + rr + 32 * q4])));
+        } else {
+          mx = fmaxf(__bfloat162float(mxbuf[(g * 2) * 128 + r]), __bfloat162float(mxbuf[(g * 2 + 1) * 128 + r]));
+        }
+        float m_new = m_prev, alpha = 1.f;  // alpha: what O (relative to m_prev) is multiplied by
+        if (mx > m_prev + TC_LAZY || (m_prev == -INFINITY && mx > -INFINITY)) {
+          alpha = m_prev == -INFINITY ? 0.f : ex2(m_prev - mx);
+          m_new = mx;
+        }
+        if (hf == 0) mrun[g * 128 + r] = m_new;
+        mbar_arrive(b_mpub + 8 * g);
+        if (m_new != m_seen) {  // this group's row sum is relative to the max it saw two tiles ago
+          l = m_seen == -INFINITY ? 0.f : l * ex2(m_seen - m_new);
+          m_seen = m_new;
+        }
+        const float sh = TC_SHIFT - (m_new == -INFINITY ? 0.f : m_new);
+        // pass 2: P = 2^(s - m + 7), e4m3 (plus the residual term while needed), into the swizzled A tiles
+        if (warp_live) {
+          const uint32_t p_hi = sP + (g * 2) * C::P_BYTES + rr * 128, p_lo = p_hi + C::P_BYTES;
+          float lsum = 0.f;
+          if (rep) {
+            uint32_t v[16];
+            tmem_ld16(s_addr, v);
+            tmem_wait_ld();
+            const uint32_t chunk0 = static_cast<uint32_t>(col_first >> 4), rx = static_cast<uint32_t>(rr & 7);
+            if (with_lo) {
+              lsum += need_mask ? exp_chunk32<true, true, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx)
+                                : exp_chunk32<false, true, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx);
+            } else {
+              lsum += need_mask ? exp_chunk32<true, false, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx)
+                                : exp_chunk32<false, false, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx);
+            }
+          }
+#pragma unroll 1
+          for (int c0 = 0; c0 < (rep ? 0 : CW); c0 += 32) {
+            const uint32_t chunk0 = static_cast<uint32_t>(hf * (CW / 16) + (c0 >> 4)), rx = static_cast<uint32_t>(r & 7);
+            if (need_mask && chunk_class(c_base + c0, pos, lo_key) == 4) {  // nothing visible: P is exactly zero here
+#pragma unroll
+              for (int c16 = 0; c16 < 2; ++c16) {
+                const uint32_t chunk = ((chunk0 + c16) ^ rx) << 4;
+                asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(p_hi + chunk), "r"(0) : "memory");
+                if (with_lo) asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(p_lo + chunk), "r"(0) : "memory");
+              }
+              continue;
+            }
+            uint32_t v[32];
+            tmem_ld32(s_addr + c0, v);  // hidden keys of a mixed chunk were set to -inf by the max pass
+            tmem_wait_ld();
+            lsum += with_lo ? exp_chunk32<false, true>(v, sl2, sh, c_base + c0, pos, lo_key, p_hi, p_lo, chunk0, rx)
+                            : exp_chunk32<false, false>(v, sl2, sh, c_base + c0, pos, lo_key, p_hi, p_lo, chunk0, rx);
+          }
+          l += lsum;
+        }
+        // S has been read for the last time: the buffer may take the scores of a later tile
+        TC_TRACE(8 + (with_lo ? 100 : 0) + (need_mask ? 50 : 0), gi);
+        tc_fence_before();
+        mbar_arrive(b_sfree + 8 * sb);
+        // The residual term of P is only needed while a row rests on few keys: once this thread's share of the row
+        // sum stands for at least 32 keys at the running max, the e4m3 rounding of P averages out far below the
+        // tolerance. The vote is for this group's next tile (read there after the wait for this tile's PV MMAs,
+        // which follow every thread's arrival below).
+        if (valid && l < 32.f * 128.f) atomicOr(lo_flag + g * 2 + ((u + 1) & 1), 1u);
+        // O in tensor memory is rescaled only when some row of this warp moved its max; needs PV of tile t-1 done.
+        if (t >= 1 && owns_o && __any_sync(0xffffffffu, alpha != 1.f)) {
+          wait_or_flag(b_pfree + 8 * (g ^ 1), ((gi - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+          tc_fence_after();
+#pragma unroll 1
+          for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+            tmem_st32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
+          }
+          tmem_wait_st();
+        }
+        // rows past the end of the sequence in the last tile: V must be finite where P is exactly 0
+        if (n0 + TNK > s.L) {
+          const int st = gi % C::NKV;
+          wait_or_flag(b_vfull + 8 * st, (gi / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
+          if (n0 + r >= s.L) {
+#pragma unroll 1
+            for (int c = hf * (C::ATOMS * 4); c < (hf + 1) * (C::ATOMS * 4); ++c) {
+              const uint32_t a = sV + st * C::KV_BYTES + (c >> 3) * SLAB + r * 128 + ((c & 7) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
+            }
           }
         }
-        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * sl2;  // sl2 > 0; -inf stays -inf
+        fence_proxy_async();
+        tc_fence_before();
+        mbar_arrive(b_pready + 8 * g);
+        TC_TRACE(9, gi);
       }
-      // both parts publish their maximum rounded UP to bf16 and take the larger (a slightly high running max
-      // only makes P a little smaller)
-      mxbuf[(g * 2 + hf) * 128 + r] = __float2bfloat16_ru(mx);
-      // What does not depend on the partner's maximum is fetched before the exchange barrier, so that these
-      // round trips overlap the wait for the slowest warp of the group: the running max after tile t - 1 from the
-      // other group, and the P buffer of this group (free once the PV MMAs of tile t - 2 are done; the residual
-      // flag of this tile is complete by then, every vote having preceded its thread's arrival for that tile).
-      float m_prev = -INFINITY;
-      if (t >= 1) {
-        wait_or_flag(b_mpub + 8 * (g ^ 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
-        m_prev = mrun[(g ^ 1) * 128 + r];
+      it = it0 + n_tiles;
+      TC_TRACE(10, it);
+      // ---- the next segment's Q goes in as soon as this thread is through its tiles: the group that finishes
+      // first does its share under the other group's last tile, and the QK lane starts the next segment's scores
+      // under this segment's output pass. The QK MMAs of this segment were issued tiles ago, so the wait for them is
+      // normally over.
+      {
+        Seg nxt;
+        if (read_seg(sk, nxt, false) && nxt.t_hi > nxt.t_lo) {
+          wait_or_flag(b_qfree, sq & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+          load_q(nxt);
+          q_ready = true;
+        }
       }
-      if (t >= 2) wait_or_flag(b_pfree + 8 * g, (u - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
-      const bool with_lo = lo_flag[g * 2 + (u & 1)] != 0u;
-      named_bar_sync(grp_bar, TC_GROUP);
-      if (rep) {  // eight shares of a row: two parts in each of the four quarters
-        mx = -INFINITY;
+      TC_TRACE(12, it);
+      // ---- end of the segment, part 1: the row sums
+      named_bar_sync(1, TC_SOFTMAX);  // all tiles of both groups are through their max exchange
+      const int gi_last = it - 1, g_last = gi_last & 1;
+      const float m_fin = mrun[g_last * 128 + r];
+      if (m_seen != m_fin) l = m_seen == -INFINITY ? 0.f : l * ex2(m_seen - m_fin);
+      named_bar_sync(1, TC_SOFTMAX);  // the row sums overlay the max buffers
+      lbuf[part * 128 + r] = l;
+      named_bar_sync(1, TC_SOFTMAX);
+      if (rep) {  // a row's sum is spread over the four parts in each of the four quarters
+        l = 0.f;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4)
-          mx = fmaxf(mx, fmaxf(__bfloat162float(mxbuf[(g * 2) * 128 + rr + 32 * q4]),
-                               __bfloat162float(mxbuf[(g * 2 + 1) * 128 + rr + 32 * q4])));
+          l += (lbuf[rr + 32 * q4] + lbuf[128 + rr + 32 * q4]) + (lbuf[256 + rr + 32 * q4] + lbuf[384 + rr + 32 * q4]);
       } else {
-        mx = fmaxf(__bfloat162float(mxbuf[(g * 2) * 128 + r]), __bfloat162float(mxbuf[(g * 2 + 1) * 128 + r]));
+        l = (lbuf[r] + lbuf[128 + r]) + (lbuf[256 + r] + lbuf[384 + r]);
       }
-      float m_new = m_prev, alpha = 1.f;  // alpha: what O (relative to m_prev) is multiplied by
-      if (mx > m_prev + TC_LAZY || (m_prev == -INFINITY && mx > -INFINITY)) {
-        alpha = m_prev == -INFINITY ? 0.f : ex2(m_prev - mx);
-        m_new = mx;
-      }
-      if (hf == 0) mrun[g * 128 + r] = m_new;
-      mbar_arrive(b_mpub + 8 * g);
-      if (m_new != m_seen) {  // this group's row sum is relative to the max it saw two tiles ago
-        l = m_seen == -INFINITY ? 0.f : l * ex2(m_seen - m_new);
-        m_seen = m_new;
-      }
-      const float sh = TC_SHIFT - (m_new == -INFINITY ? 0.f : m_new);
-      // pass 2: P = 2^(s - m + 7), e4m3 (plus the residual term while needed), into the swizzled A tiles
-      if (warp_live) {
-        const uint32_t p_hi = sP + (g * 2) * C::P_BYTES + rr * 128, p_lo = p_hi + C::P_BYTES;
-        float lsum = 0.f;
-        if (rep) {
-          uint32_t v[16];
-          tmem_ld16(s_addr, v);
-          tmem_wait_ld();
-          const uint32_t chunk0 = static_cast<uint32_t>(col_first >> 4), rx = static_cast<uint32_t>(rr & 7);
-          if (with_lo) {
-            lsum += need_mask ? exp_chunk32<true, true, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx)
-                              : exp_chunk32<false, true, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx);
-          } else {
-            lsum += need_mask ? exp_chunk32<true, false, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx)
-                              : exp_chunk32<false, false, 16>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx);
-          }
-        }
-#pragma unroll 1
-        for (int c0 = 0; c0 < (rep ? 0 : CW); c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(s_addr + c0, v);
-          tmem_wait_ld();
-          const uint32_t chunk0 = static_cast<uint32_t>(hf * (CW / 16) + (c0 >> 4)), rx = static_cast<uint32_t>(r & 7);
-          if (with_lo) {
-            lsum += need_mask ? exp_chunk32<true, true>(v, sl2, sh, c_base + c0, pos, lo_key, p_hi, p_lo, chunk0, rx)
-                              : exp_chunk32<false, true>(v, sl2, sh, c_base + c0, pos, lo_key, p_hi, p_lo, chunk0, rx);
-          } else {
-            lsum += need_mask ? exp_chunk32<true, false>(v, sl2, sh, c_base + c0, pos, lo_key, p_hi, p_lo, chunk0, rx)
-                              : exp_chunk32<false, false>(v, sl2, sh, c_base + c0, pos, lo_key, p_hi, p_lo, chunk0, rx);
-          }
-        }
-        l += lsum;
-      }
-      // S has been read for the last time: the buffer may take the scores of tile t + 2
-      tc_fence_before();
-      mbar_arrive(b_sfree + 8 * sb);
-      // The residual term of P is only needed while a row rests on few keys: once this thread's share of the row
-      // sum stands for at least 32 keys at the running max, the e4m3 rounding of P averages out far below the
-      // tolerance. The vote is for this group's next tile (read there after the wait for this tile's PV MMAs,
-      // which follow every thread's arrival below).
-      if (valid && l < 32.f * 128.f) atomicOr(lo_flag + g * 2 + ((u + 1) & 1), 1u);
-      // O in tensor memory is rescaled only when some row of this warp moved its max; needs PV of tile t-1 done.
-      if (t >= 1 && owns_o && __any_sync(0xffffffffu, alpha != 1.f)) {
-        wait_or_flag(b_pfree + 8 * (g ^ 1), ((t - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
-        tc_fence_after();
-#pragma unroll 1
-        for (int c0 = 0; c0 < HD / 2; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-          tmem_st32(lane_base + C::O_COL + hf * (HD / 2) + c0, v);
-        }
-        tmem_wait_st();
-      }
-      // rows past the end of the sequence in the last tile: V must be finite where P is exactly 0
-      if (n0 + TNK > s.L) {
-        const int st = t % C::NKV;
-        wait_or_flag(b_vfull + 8 * st, (t / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
-        if (n0 + r >= s.L) {
-#pragma unroll 1
-          for (int c = hf * (C::ATOMS * 4); c < (hf + 1) * (C::ATOMS * 4); ++c) {
-            const uint32_t a = sV + st * C::KV_BYTES + (c >> 3) * SLAB + r * 128 + ((c & 7) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
-          }
-        }
-      }
-      fence_proxy_async();
-      tc_fence_before();
-      mbar_arrive(b_pready + 8 * g);
-    }
-    // ---- epilogue: O / l, each thread one quarter of the output dims of its row
-    named_bar_sync(1, TC_SOFTMAX);  // all tiles of both groups are through their max exchange
-    const int g_last = (n_tiles - 1) & 1;
-    const float m_fin = n_tiles > 0 ? mrun[g_last * 128 + r] : -INFINITY;
-    if (m_seen != m_fin) l = m_seen == -INFINITY ? 0.f : l * ex2(m_seen - m_fin);
-    named_bar_sync(1, TC_SOFTMAX);  // the row sums overlay the max buffers
-    lbuf[part * 128 + r] = l;
-    named_bar_sync(1, TC_SOFTMAX);
-    if (rep) {  // a row's sum is spread over the four parts in each of the four quarters
-      l = 0.f;
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4)
-        l += (lbuf[rr + 32 * q4] + lbuf[128 + rr + 32 * q4]) + (lbuf[256 + rr + 32 * q4] + lbuf[384 + rr + 32 * q4]);
-    } else {
-      l = (lbuf[r] + lbuf[128 + r]) + (lbuf[256 + r] + lbuf[384 + r]);
-    }
-    if (n_tiles > 0) {
-      wait_or_flag(b_pfree + 8 * g_last, ((n_tiles - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      named_bar_sync(1, TC_SOFTMAX);  // the sums are read: the next segment may write the max buffers again
+      TC_TRACE(11, it);
+      // ---- part 2: O / l, each thread one quarter of the output dims of its row
+      wait_or_flag(b_pfree + 8 * g_last, (gi_last >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      TC_TRACE(13, it);
       tc_fence_after();
-    }
-    const bool bad = __any_sync(0xffffffffu, failed);  // tensor-memory loads are warp-collective
-    const float inv = l > 0.f ? vds / l : 0.f;
-    const long long ooff = static_cast<long long>(s.q0 + tq) * p.o_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.o_s1 +
-                           part * (HD / 4);
+      const bool bad = __any_sync(0xffffffffu, failed);  // tensor-memory loads are warp-collective
+      const bool partial = s.slot >= 0;  // a piece of a unit that other CTAs share: fp32 into the workspace slot
+      const int tq = rr / p.gqa, hq = rr - tq * p.gqa;
+      const long long ooff = static_cast<long long>(s.q0 + tq) * p.o_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.o_s1 +
+                             part * (HD / 4);
+      const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
+      const float inv = l > 0.f ? (partial ? 1.f : vds) / l : 0.f;
+      if (!rep && !partial) {
+        // bf16 rows go through a warp-private patch of shared memory (this group's P buffers: every MMA that read
+        // them has completed, and no warp of the group writes P again before all of them are past this point) so
+        // that the global stores are whole 64- or 128-byte runs of a row instead of 16 bytes from each of 32 rows.
+        constexpr int CH = HD / 32;   // 16-byte chunks of this thread's quarter row
+        constexpr int ROWB = CH * 16;
+        const uint32_t stage = sP + (g * 2) * C::P_BYTES + (warp & 7) * (32 * ROWB);
 #pragma unroll 1
-    for (int c0 = 0; c0 < (owns_o ? HD / 4 : 0); c0 += 32) {
-      uint32_t v[32];
-      if (n_tiles > 0 && !bad) {
-        tmem_ld32(lane_base + C::O_COL + part * (HD / 4) + c0, v);
-        tmem_wait_ld();
-      } else {
+        for (int c0 = 0; c0 < HD / 4; c0 += 32) {
+          uint32_t v[32];
+          if (!bad) {
+            tmem_ld32(lane_base + C::O_COL + part * (HD / 4) + c0, v);
+            tmem_wait_ld();
+          } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = 0u;
-      }
-      if (valid) {
-        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + ooff + c0;
-#pragma unroll
-        for (int q8 = 0; q8 < 4; ++q8) {
-          uint32_t w[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[q8 * 8 + 2 * j]) * inv,
-                                                      __uint_as_float(v[q8 * 8 + 2 * j + 1]) * inv);
-            w[j] = *reinterpret_cast<uint32_t*>(&b2);
+            for (int j = 0; j < 32; ++j) v[j] = 0u;
           }
-          *reinterpret_cast<uint4*>(dst + q8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+#pragma unroll
+          for (int q8 = 0; q8 < 4; ++q8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[q8 * 8 + 2 * j]) * inv,
+                                                        __uint_as_float(v[q8 * 8 + 2 * j + 1]) * inv);
+              w[j] = *reinterpret_cast<uint32_t*>(&b2);
+            }
+            const uint32_t dst = stage + lane * ROWB + ((((c0 >> 3) + q8) ^ (lane & (CH - 1))) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                         : "memory");
+          }
         }
+        // O has been read: the PV lane may start the next segment's accumulation
+        tc_fence_before();
+        mbar_arrive(b_ofree);
+        TC_TRACE(14, it);
+        __syncwarp();
+        const long long row_off = valid ? ooff : -1;
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+          const int row = i * (32 / CH) + lane / CH, j = lane % CH;
+          uint4 w;
+          asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                       : "r"(stage + row * ROWB + ((j ^ (row & (CH - 1))) << 4)));
+          const long long o = __shfl_sync(0xffffffffu, row_off, row);
+          if (o >= 0) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + o + j * 8) = w;
+        }
+        __syncwarp();
+        TC_TRACE(15, it);
+      } else {
+        float* wdst = partial ? p.ws_o + (static_cast<long long>(s.slot) * p.rows_cap + rr) * HD + part * (HD / 4) : nullptr;
+#pragma unroll 1
+        for (int c0 = 0; c0 < (owns_o ? HD / 4 : 0); c0 += 32) {
+          uint32_t v[32];
+          if (!bad) {
+            tmem_ld32(lane_base + C::O_COL + part * (HD / 4) + c0, v);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0u;
+          }
+          if (valid && partial) {
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4)
+              *reinterpret_cast<float4*>(wdst + c0 + q4 * 4) =
+                  make_float4(__uint_as_float(v[q4 * 4]) * inv, __uint_as_float(v[q4 * 4 + 1]) * inv,
+                              __uint_as_float(v[q4 * 4 + 2]) * inv, __uint_as_float(v[q4 * 4 + 3]) * inv);
+          } else if (valid) {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + ooff + c0;
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[q8 * 8 + 2 * j]) * inv,
+                                                          __uint_as_float(v[q8 * 8 + 2 * j + 1]) * inv);
+                w[j] = *reinterpret_cast<uint32_t*>(&b2);
+              }
+              *reinterpret_cast<uint4*>(dst + q8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+        // O has been read: the PV lane may start the next segment's accumulation
+        tc_fence_before();
+        mbar_arrive(b_ofree);
+        TC_TRACE(14, it);
       }
-    }
-    if (valid && owns_o && part == 0 && p.lse != nullptr) {
-      p.lse[static_cast<long long>(s.h * p.gqa + hq) * p.total_q + s.q0 + tq] =
-          l > 0.f ? (m_fin + lg2(l) - TC_SHIFT) * 0.6931471805599453f : -INFINITY;
+      if (valid && owns_o && part == 0) {
+        const float lse2 = l > 0.f ? m_fin + lg2(l) - TC_SHIFT : -INFINITY;
+        if (partial) p.ws_lse[static_cast<long long>(s.slot) * p.rows_cap + rr] = lse2;
+        else if (p.lse != nullptr)
+          p.lse[static_cast<long long>(s.h * p.gqa + hq) * p.total_q + s.q0 + tq] = lse2 * 0.6931471805599453f;
+      }
+      ++sq;
     }
   }
   tc_fence_before();

@@ -17,13 +17,13 @@ enum : int {
   GA_ST_LEN_RANGE = 5  // a cache_seqlens entry exceeds pt_cols * page_size
 };
 
-// Upper bound on polls of one barrier wait. A poll of try_wait may itself block for a
-// hardware-defined interval, so this bounds a stuck wait to seconds, after which the kernel records
-// where it gave up and returns instead of spinning forever.
-constexpr uint32_t kMaxPolls = 1u << 22;
 // Upper bound (ns) a single try_wait may keep the thread suspended before it polls again: waiting warps then
 // take almost no issue slots from the warps that compute.
 constexpr uint32_t kSuspendHintNs = 20000;
+// Upper bound on polls of one barrier wait. A poll that finds the phase incomplete suspends the thread for at
+// most kSuspendHintNs, so a stuck wait gives up after at most 1.3 s (less if the hardware wakes the thread
+// earlier), records where and returns instead of spinning forever. A healthy wait here lasts microseconds.
+constexpr uint32_t kMaxPolls = 1u << 16;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -54,6 +54,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: true when the phase completed, false when the poll budget ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+#pragma unroll 1
   for (uint32_t i = 0; i < kMaxPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
