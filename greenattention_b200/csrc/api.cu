@@ -15,6 +15,7 @@
 #include "../../include/green_attention.h"
 #include "attn_rows.cuh"
 #include "attn_tc.cuh"
+#include "attn_wide.cuh"
 #include "gdn_recurrent.cuh"
 #include "gdn_verify.cuh"
 
@@ -53,6 +54,7 @@ struct MapKey {
   const void* base;
   long long s_page, s_tok, s_head;
   int pages, page, kvh, hd, box_tok;
+  int all_heads;  // 1: dimensions listed as (dim, token, head, page) with a box of box_tok tokens x all heads
   bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
 };
 struct MapEntry {
@@ -75,6 +77,12 @@ int get_map(const MapKey& key, CUtensorMap* out) {
   cuuint64_t dims[4] = {(cuuint64_t)key.hd, (cuuint64_t)key.kvh, (cuuint64_t)key.page, (cuuint64_t)key.pages};
   cuuint64_t strides[3] = {(cuuint64_t)key.s_head, (cuuint64_t)key.s_tok, (cuuint64_t)key.s_page};
   cuuint32_t box[4] = {128, 1, (cuuint32_t)key.box_tok, 1};
+  if (key.all_heads) {
+    // Token before head: the box then lands in shared memory head-major, each head's rows swizzled by token.
+    dims[1] = (cuuint64_t)key.page, dims[2] = (cuuint64_t)key.kvh;
+    strides[0] = (cuuint64_t)key.s_tok, strides[1] = (cuuint64_t)key.s_head;
+    box[1] = (cuuint32_t)key.box_tok, box[2] = (cuuint32_t)key.kvh;
+  }
   cuuint32_t estr[4] = {1, 1, 1, 1};
   MapEntry e;
   std::memset(&e, 0, sizeof(e));
@@ -183,6 +191,8 @@ int set_smem(const AttnInstance& k) {
 
 // Raises the dynamic shared memory limit of every kernel instance on the current device.
 int set_all_smem_limits() {
+  GA_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(ga::attn::attn_wide_kernel),
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, ga::attn::SMEM_OPTIN));
   for (int hd : {128, 256}) {
     for (int rows : {8, 16, 24, 32, 64, 128})
       if (set_smem(*decode_instance(hd, rows))) return 1;
@@ -265,9 +275,9 @@ int fill_attn(const GaAttnParams* a, ga::attn::AttnDev* d, CUtensorMap* kmap, CU
   std::memset(vmap, 0, sizeof(*vmap));
   if (d->use_tma) {
     MapKey kk = {a->k_cache, a->k_stride_page, a->k_stride_tok, a->k_stride_head, a->num_pages, a->page_size,
-                 a->kv_heads, a->head_dim, d->box_tok};
+                 a->kv_heads, a->head_dim, d->box_tok, 0};
     MapKey vk = {a->v_cache, a->v_stride_page, a->v_stride_tok, a->v_stride_head, a->num_pages, a->page_size,
-                 a->kv_heads, a->head_dim, d->box_tok};
+                 a->kv_heads, a->head_dim, d->box_tok, 0};
     if (get_map(kk, kmap) || get_map(vk, vmap)) return 1;
   }
   return 0;
@@ -388,18 +398,35 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
     GA_CUDA(cudaGetLastError());
     dim3 tgrid(a->batch, a->kv_heads);
     if (a->head_dim == 128)
-      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, tgrid, dim3(128), 0, st, d, sm, d.rows_cap, ga::attn::tc::TNK));
+      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, tgrid, dim3(128), 0, st, d, sm, d.rows_cap, ga::attn::tc::TNK, 0));
     else
-      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, tgrid, dim3(128), 0, st, d, sm, d.rows_cap, ga::attn::tc::TNK));
+      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, tgrid, dim3(128), 0, st, d, sm, d.rows_cap, ga::attn::tc::TNK, 0));
+    g_launches = 2;
+    return 0;
+  }
+  dim3 cgrid(a->batch, a->kv_heads);
+  // The production decode shape (at most 8 rows per kv head, head_dim 128, 4..8 kv heads, pages of at least 32
+  // tokens) gathers all kv heads of a token run per TMA box: contiguous 16 - 32 KB runs of a page stream about a
+  // fifth faster than one head's 128-byte pieces. GREEN_ATTN_NO_WIDE=1 keeps such calls on the per-head kernel.
+  static const bool no_wide = [] { const char* e = std::getenv("GREEN_ATTN_NO_WIDE"); return e && e[0] == '1'; }();
+  if (!no_wide && rows <= 8 && a->head_dim == 128 && d.use_tma && a->page_size >= ga::attn::WIDE_T && a->kv_heads >= 4 &&
+      a->kv_heads <= ga::attn::WIDE_HEADS) {
+    MapKey kk = {a->k_cache, a->k_stride_page, a->k_stride_tok, a->k_stride_head, a->num_pages, a->page_size,
+                 a->kv_heads, a->head_dim, ga::attn::WIDE_T, 1};
+    MapKey vk = {a->v_cache, a->v_stride_page, a->v_stride_tok, a->v_stride_head, a->num_pages, a->page_size,
+                 a->kv_heads, a->head_dim, ga::attn::WIDE_T, 1};
+    if (get_map(kk, &kmap) || get_map(vk, &vmap)) return 1;
+    GA_CUDA(launch_pdl(ga::attn::attn_wide_kernel, dim3(sm), dim3(ga::attn::WIDE_THREADS),
+                       static_cast<size_t>(ga::attn::wide_smem_bytes(a->kv_heads)), st, d, kmap, vmap));
+    GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, cgrid, dim3(128), 0, st, d, sm, ga::attn::WIDE_ROWS, ga::attn::WIDE_T, 1));
     g_launches = 2;
     return 0;
   }
   const AttnInstance* k = decode_instance(a->head_dim, rows);
   const int grid = sm * k->occ;
   GA_CUDA(launch_pdl(k->fn, dim3(grid), dim3(k->threads), k->smem, st, d, kmap, vmap));
-  dim3 cgrid(a->batch, a->kv_heads);
-  if (a->head_dim == 128) GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN));
-  else GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN));
+  if (a->head_dim == 128) GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN, 0));
+  else GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN, 0));
   g_launches = 2;
   return 0;
 }

@@ -139,12 +139,15 @@ struct Seg {
 struct SliceWalker {
   long long g0, g1, u0;
   int b, h, cnt, tlo, L, ql;
-  int cta, tile;
+  int cta, tile, kvh;
   bool live;
 
-  __device__ void init(const AttnDev& p, int cta_, int G, int lane, int tile_ = TN) {
+  // `heads`: units per request. The kv heads of the call when a unit is one (request, kv head); 1 when a unit is a
+  // whole request and every tile carries all kv heads (the all-heads decode kernel), in which case s.h stays 0.
+  __device__ void init(const AttnDev& p, int cta_, int G, int lane, int tile_ = TN, int heads = 0) {
     cta = cta_;
     tile = tile_;
+    kvh = heads > 0 ? heads : p.kvh;
     long long sum = 0;
     for (int b0 = 0; b0 < p.batch; b0 += 32) {
       int bb = b0 + lane;
@@ -152,7 +155,7 @@ struct SliceWalker {
     }
 #pragma unroll
     for (int d = 16; d; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-    long long T = sum * p.kvh;
+    long long T = sum * kvh;
     g0 = slice_start(T, G, cta);
     g1 = slice_start(T, G, cta + 1);
     live = g1 > g0;
@@ -163,7 +166,7 @@ struct SliceWalker {
       int bb = b0 + lane;
       int c = bb < p.batch ? seq_info(p, bb, tile).cnt : 0;
       int incl = warp_incl_scan(c, lane);
-      unsigned hit = __ballot_sync(0xffffffffu, (pre + incl) * p.kvh > g0);
+      unsigned hit = __ballot_sync(0xffffffffu, (pre + incl) * kvh > g0);
       if (hit) {
         int src = __ffs(hit) - 1;
         int incl_s = __shfl_sync(0xffffffffu, incl, src);
@@ -179,8 +182,8 @@ struct SliceWalker {
       return;
     }
     load(p);
-    h = static_cast<int>((g0 - pre * p.kvh) / cnt);
-    u0 = pre * p.kvh + static_cast<long long>(h) * cnt;
+    h = static_cast<int>((g0 - pre * kvh) / cnt);
+    u0 = pre * kvh + static_cast<long long>(h) * cnt;
   }
   __device__ void load(const AttnDev& p) {
     SeqInfo s = seq_info(p, b, tile);
@@ -207,7 +210,7 @@ struct SliceWalker {
     u0 = u1;
     if (u0 >= g1) {
       live = false;
-    } else if (++h == p.kvh) {
+    } else if (++h == kvh) {
       h = 0;
       do {
         ++b;
@@ -697,28 +700,32 @@ __device__ __forceinline__ void load_q_frags8(const AttnDev& p, const Seg& s, in
   }
 }
 
-template <class C>
-__device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, int tt, uint32_t stage_addr,
+// NT: tokens of the tile (a multiple of 32); K rows at `k_addr`, V rows at `v_addr`, each NT x 128 bytes per
+// 128-dim slab, swizzled by token.
+template <class C, int NT = TN>
+__device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, int n0, uint32_t k_addr, uint32_t v_addr,
                                               const uint32_t (&qf)[C::ATOMS * 4][2], int pos, float sl2,
                                               RowAcc8<C>& acc, int lane) {
+  static_assert(NT % 32 == 0, "tile length");
+  constexpr int SLABB = NT * 128;  // bytes between the 128-dim slabs of a wider head
+  constexpr int NG = NT / 8;       // 8-token groups
   const int t = lane & 3;
-  const int n0 = tt * TN;
   const int lrow = lane & 7, lmat = lane >> 3;
   const uint32_t xr = static_cast<uint32_t>(lrow) << 4;
 
-  float sc[8][4];
+  float sc[NG][4];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+  for (int j = 0; j < NG; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
+  for (int half = 0; half < NT / 32; ++half) {
     uint32_t kb[4][C::ATOMS * 2][4];
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
-      const uint32_t rowaddr = stage_addr + ((half * 4 + jj) * 8 + lrow) * 128;
+      const uint32_t rowaddr = k_addr + ((half * 4 + jj) * 8 + lrow) * 128;
 #pragma unroll
       for (int q4 = 0; q4 < C::ATOMS * 2; ++q4) {
         const int c = q4 * 4 + lmat;
-        ldsm_x4(rowaddr + (c >> 3) * ATOM_BYTES + ((static_cast<uint32_t>(c & 7) << 4) ^ xr), kb[jj][q4][0],
+        ldsm_x4(rowaddr + (c >> 3) * SLABB + ((static_cast<uint32_t>(c & 7) << 4) ^ xr), kb[jj][q4][0],
                 kb[jj][q4][1], kb[jj][q4][2], kb[jj][q4][3]);
       }
     }
@@ -735,12 +742,12 @@ __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, in
     }
   }
 
-  const bool need_mask = (n0 + TN > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
+  const bool need_mask = (n0 + NT > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
   float mx = -INFINITY;
   if (need_mask) {
     const int lo = p.window_left >= 0 ? pos - p.window_left : -(1 << 30);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < NG; ++j) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int col = n0 + j * 8 + t * 2 + e;
@@ -750,19 +757,19 @@ __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, in
         mx = fmaxf(mx, a);
       }
     }
-    if (n0 + TN > s.L) {  // stale rows past the end of the sequence: make V finite where P is exactly 0
+    if (n0 + NT > s.L) {  // stale rows past the end of the sequence: make V finite where P is exactly 0
       int first = s.L - n0;
       if (first < 0) first = 0;
-      for (int idx = first * (C::ATOMS * 8) + lane; idx < TN * C::ATOMS * 8; idx += 32) {
+      for (int idx = first * (C::ATOMS * 8) + lane; idx < NT * C::ATOMS * 8; idx += 32) {
         int row = idx / (C::ATOMS * 8), c = idx - row * (C::ATOMS * 8);
-        uint32_t a = stage_addr + C::V_OFF + (c >> 3) * ATOM_BYTES + row * 128 + ((c & 7) << 4);
+        uint32_t a = v_addr + (c >> 3) * SLABB + row * 128 + ((c & 7) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
       }
       __syncwarp();
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < NG; ++j) {
       sc[j][0] *= sl2;
       sc[j][1] *= sl2;
       mx = fmaxf(mx, fmaxf(sc[j][0], sc[j][1]));
@@ -787,9 +794,9 @@ __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, in
   }
   // P = 2^(s - m + 8), split into two e4m3 terms (4 significant bits + residual), see the general path.
   const float sh = P_SHIFT - mu;
-  uint32_t ph[8], pl[8];
+  uint32_t ph[NG], pl[NG];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < NG; ++j) {
     float e0 = ex2(sc[j][0] + sh), e1 = ex2(sc[j][1] + sh);
     acc.l += e0 + e1;
     float h0 = __uint_as_float((__float_as_uint(e0) + 0x00080000u) & 0xfff00000u);
@@ -797,9 +804,9 @@ __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, in
     ph[j] = pack_e4m3x2(h0, h1);
     pl[j] = pack_e4m3x2(e0 - h0, e1 - h1);
   }
-  const uint32_t vbase = stage_addr + C::V_OFF;
+  const uint32_t vbase = v_addr;
 #pragma unroll
-  for (int c2 = 0; c2 < 2; ++c2) {
+  for (int c2 = 0; c2 < NT / 32; ++c2) {
     const uint32_t bh0 = ph[c2 * 4] | (ph[c2 * 4 + 1] << 16), bh1 = ph[c2 * 4 + 2] | (ph[c2 * 4 + 3] << 16);
     const uint32_t bl0 = pl[c2 * 4] | (pl[c2 * 4 + 1] << 16), bl1 = pl[c2 * 4 + 2] | (pl[c2 * 4 + 3] << 16);
     const uint32_t rowaddr = vbase + ((c2 * 4 + lmat) * 8 + lrow) * 128;
@@ -809,7 +816,7 @@ __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, in
 #pragma unroll
       for (int d8 = 0; d8 < 8; ++d8) {
         uint32_t r0, r1, r2, r3;
-        ldsm_x4_trans(rowaddr + grp * ATOM_BYTES + ((static_cast<uint32_t>(d8) << 4) ^ xr), r0, r1, r2, r3);
+        ldsm_x4_trans(rowaddr + grp * SLABB + ((static_cast<uint32_t>(d8) << 4) ^ xr), r0, r1, r2, r3);
         va[d8][0] = prmt(r0, r1, 0x6420);
         va[d8][1] = prmt(r0, r1, 0x7531);
         va[d8][2] = prmt(r2, r3, 0x6420);
@@ -952,7 +959,8 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
         if (failed) continue;
 #pragma unroll 1
         for (int u = 0; u < C::SUB && tt + u < s.t_hi; ++u)
-          consume_tile8<C>(p, s, tt + u, ring + stage * C::STAGE_BYTES + u * C::TILE_BYTES, qf, pos, sl2, acc, lane);
+          consume_tile8<C>(p, s, (tt + u) * TN, ring + stage * C::STAGE_BYTES + u * C::TILE_BYTES,
+                           ring + stage * C::STAGE_BYTES + u * C::TILE_BYTES + C::V_OFF, qf, pos, sl2, acc, lane);
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + (C::NST + stage) * 8);
@@ -1143,9 +1151,11 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
 // Combine: one CTA per (request, kv head). Writes zeros / -inf for requests without keys, leaves units
 // that a single CTA finished alone, and merges the partials of split units in slice order
 // (math of the reference's combine kernel, kernel.cuh:665-749; no atomics, so bit-reproducible).
+// `wide`: the partials come from the all-heads decode kernel: a unit is a whole request (so every kv head of a
+// request was cut at the same tiles) and a slot holds 8 rows per kv head, head-major.
 template <int HD>
 __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant__ AttnDev p, int G, int rows_cap,
-                                                          int tile) {
+                                                          int tile, int wide = 0) {
   const int b = blockIdx.x, h = blockIdx.y;
   grid_dep_wait();    // the whole decode grid has finished and its partials are visible
   grid_dep_launch();  // the next kernel in the stream may start its own prologue
@@ -1168,8 +1178,10 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
     }
     return;
   }
-  const long long T = static_cast<long long>(p.prefix[p.batch]) * p.kvh;
-  const long long u0 = static_cast<long long>(p.prefix[b]) * p.kvh + static_cast<long long>(h) * si.cnt;
+  const int upr = wide ? 1 : p.kvh;      // units per request
+  const int rbase = wide ? 8 * h : 0;    // first row of this kv head inside a slot
+  const long long T = static_cast<long long>(p.prefix[p.batch]) * upr;
+  const long long u0 = static_cast<long long>(p.prefix[b]) * upr + (wide ? 0 : static_cast<long long>(h) * si.cnt);
   const long long u1 = u0 + si.cnt;
   auto cta_of = [&](long long x) {
     long long c = ((x + 1) * G - 1) / T;
@@ -1199,7 +1211,7 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
 #pragma unroll 4
     for (int i = 0; i < n_list; ++i) {
       const int slot = slot_list[i];
-      if (slot >= 0) mx = fmaxf(mx, __ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + r));
+      if (slot >= 0) mx = fmaxf(mx, __ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + rbase + r));
     }
     float den = 0.f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -1208,8 +1220,8 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
       for (int i = 0; i < n_list; ++i) {
         const int slot = slot_list[i];
         if (slot < 0) continue;
-        float w = ex2(__ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + r) - mx);
-        float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (static_cast<long long>(slot) * rows_cap + r) * HD + d));
+        float w = ex2(__ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + rbase + r) - mx);
+        float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (static_cast<long long>(slot) * rows_cap + rbase + r) * HD + d));
         den += w;
         o.x += w * v.x;
         o.y += w * v.y;
