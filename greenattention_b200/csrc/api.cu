@@ -394,13 +394,18 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
     const AttnInstance* tk = rep ? verify_tc_instance(a->head_dim) : extend_tc_instance(a->head_dim);
     d.tc_mode = 0;
     d.rows_cap = rep ? 32 : ga::attn::MAX_ROWS;
-    tk->fn<<<sm, tk->threads, tk->smem, st>>>(d, kmap, vmap);
+    // Gangs of kv_heads CTAs walk the same pages at the same time, one kv head each (see TcWork); a few SMs stay
+    // idle when kv_heads does not divide their number, which the faster gather more than pays for.
+    d.gang = (a->kv_heads >= 2 && a->kv_heads <= 16 && sm / a->kv_heads >= 1) ? 1 : 0;
+    const int tgrid_x = d.gang ? sm / a->kv_heads * a->kv_heads : sm;
+    tk->fn<<<tgrid_x, tk->threads, tk->smem, st>>>(d, kmap, vmap);
     GA_CUDA(cudaGetLastError());
     dim3 tgrid(a->batch, a->kv_heads);
+    const int wide_mode = d.gang ? 2 : 0;
     if (a->head_dim == 128)
-      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, tgrid, dim3(128), 0, st, d, sm, d.rows_cap, ga::attn::tc::TNK, 0));
+      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, tgrid, dim3(128), 0, st, d, tgrid_x, d.rows_cap, ga::attn::tc::TNK, wide_mode));
     else
-      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, tgrid, dim3(128), 0, st, d, sm, d.rows_cap, ga::attn::tc::TNK, 0));
+      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, tgrid, dim3(128), 0, st, d, tgrid_x, d.rows_cap, ga::attn::tc::TNK, wide_mode));
     g_launches = 2;
     return 0;
   }

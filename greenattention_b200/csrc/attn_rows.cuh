@@ -69,6 +69,7 @@ struct AttnDev {
   int tc_mode;       // tcgen05 kernel: 0 = slices of the tile stream (decode / verify route), 1 = extend items
   int nblk;          // tcgen05 extend: the host's upper bound on the number of query blocks
   int rows_cap;      // rows per workspace slot (row stride of ws_o / ws_lse)
+  int gang;          // tcgen05 kernel, mode 0: CTAs work in gangs of kv_heads on slices of whole requests
   // split-KV workspace
   int* status;
   int* prefix;       // [batch + 1] exclusive prefix of per-request tile counts (written by CTA 0)
@@ -1151,8 +1152,10 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
 // Combine: one CTA per (request, kv head). Writes zeros / -inf for requests without keys, leaves units
 // that a single CTA finished alone, and merges the partials of split units in slice order
 // (math of the reference's combine kernel, kernel.cuh:665-749; no atomics, so bit-reproducible).
-// `wide`: the partials come from the all-heads decode kernel: a unit is a whole request (so every kv head of a
-// request was cut at the same tiles) and a slot holds 8 rows per kv head, head-major.
+// `wide` = 1: the partials come from the all-heads decode kernel: a unit is a whole request (so every kv head of a
+// request was cut at the same tiles) and a slot holds 8 rows per kv head, head-major. `wide` = 2: they come from
+// ganged CTAs of the tcgen05 kernel: a unit is a whole request, slices belong to the G / kv_heads gangs, and the
+// slots of kv head h in gang c are those of CTA c * kv_heads + h.
 template <int HD>
 __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant__ AttnDev p, int G, int rows_cap,
                                                           int tile, int wide = 0) {
@@ -1178,8 +1181,10 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
     }
     return;
   }
-  const int upr = wide ? 1 : p.kvh;      // units per request
-  const int rbase = wide ? 8 * h : 0;    // first row of this kv head inside a slot
+  const int upr = wide ? 1 : p.kvh;         // units per request
+  const int rbase = wide == 1 ? 8 * h : 0;  // first row of this kv head inside a slot
+  const int cta_mul = wide == 2 ? p.kvh : 1, cta_add = wide == 2 ? h : 0;  // CTA that ran slice c for this kv head
+  if (wide == 2) G /= p.kvh;                // slices = gangs
   const long long T = static_cast<long long>(p.prefix[p.batch]) * upr;
   const long long u0 = static_cast<long long>(p.prefix[b]) * upr + (wide ? 0 : static_cast<long long>(h) * si.cnt);
   const long long u1 = u0 + si.cnt;
@@ -1193,7 +1198,7 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
   };
   const int c0 = cta_of(u0), c1 = cta_of(u1 - 1);
   if (c0 == c1) return;
-  const int slot0 = 2 * c0 + (u0 <= slice_start(T, G, c0) ? 0 : 1);
+  const int slot0 = 2 * (c0 * cta_mul + cta_add) + (u0 <= slice_start(T, G, c0) ? 0 : 1);
   // The workspace slot of every CTA that holds a piece of this unit, worked out once (a long sequence at a small
   // batch is cut into dozens of slices; the slice bounds cost a 64-bit division each).
   constexpr int MAX_LIST = 1024;
@@ -1202,7 +1207,7 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
   for (int i = threadIdx.x; i < n_list; i += blockDim.x) {
     const int c = c0 + i;
     const bool empty = slice_start(T, G, c + 1) == slice_start(T, G, c);  // a CTA with an empty slice wrote nothing
-    slot_list[i] = empty ? -1 : (c == c0 ? slot0 : 2 * c);
+    slot_list[i] = empty ? -1 : (c == c0 ? slot0 : 2 * (c * cta_mul + cta_add));
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < rows * (HD / 4); idx += blockDim.x) {

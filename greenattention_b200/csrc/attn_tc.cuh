@@ -241,10 +241,14 @@ constexpr int SEG_WORDS = 10;    // b, h, q0, nq, pos0, L, t_lo, t_hi, slot, val
 constexpr int SEG_READERS = 22;  // warps that consume every segment: 16 softmax, 4 producers, 2 issuing
 
 // Work source of a persistent CTA, run by its scheduler warp (all 32 lanes call next()).
-//   mode 0 (decode / verify route): the call is one stream of 128-key tiles ordered by (request, kv head) and CTA c
-//     takes the contiguous slice [c T / G, (c + 1) T / G) of it, exactly as the warp-level decode kernel does, so
-//     any batch and any mix of lengths balances to one tile; a unit that a slice cuts is finished by the combine
-//     kernel from the partial (O, LSE) the CTAs leave in the workspace slots.
+//   mode 0 (decode / verify route): the call is one stream of 128-key tiles and contiguous slices of it go to the
+//     CTAs, exactly as in the warp-level decode kernel, so any batch and any mix of lengths balances to one tile; a
+//     unit that a slice cuts is finished by the combine kernel from the partial (O, LSE) the CTAs leave in the
+//     workspace slots. With `p.gang` the CTAs work in gangs of kv_heads: a unit is a whole request, a slice belongs
+//     to a gang, and CTA (gang, h) runs kv head h of it. The kv heads of a page (128-byte pieces of each token's
+//     kv_heads * 128 bytes) are then fetched by neighbouring SMs at the same time, and DRAM sees the contiguous run
+//     of the page instead of one piece in eight: measured 6.8 - 7.1 TB/s against 5.3 - 5.8 TB/s for the same gather
+//     with every CTA on its own (request, kv head) units.
 //   mode 1 (extend): items are (query block, kv head) pairs, latest (heaviest) blocks first; item i is block
 //     i % nblk of kv head i / nblk, where nblk is the host's upper bound on the number of blocks (items past the
 //     real count are skipped). CTAs claim items one at a time from a counter in the workspace header, so SMs that
@@ -258,10 +262,18 @@ struct TcWork {
     nblk = p.nblk;
     item_end = p.nblk * p.kvh;
     counters = p.status + 1;
-    if (mode == 0) walk.init(p, blockIdx.x, gridDim.x, lane, TNK);
+    if (mode == 0 && p.gang) walk.init(p, blockIdx.x / p.kvh, gridDim.x / p.kvh, lane, TNK, 1);
+    else if (mode == 0) walk.init(p, blockIdx.x, gridDim.x, lane, TNK);
   }
   __device__ bool next(const AttnDev& p, int lane, Seg& s) {
-    if (mode == 0) return walk.next(p, s);
+    if (mode == 0) {
+      if (!walk.next(p, s)) return false;
+      if (p.gang) {  // the walker speaks of gangs and whole requests: this CTA's kv head and its own slots
+        s.h = blockIdx.x % p.kvh;
+        if (s.slot >= 0) s.slot = 2 * static_cast<int>(blockIdx.x) + (s.slot & 1);
+      }
+      return true;
+    }
     while (true) {
       int i = 0;
       if (lane == 0) i = atomicAdd(counters, 1);
