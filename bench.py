@@ -46,7 +46,7 @@ ATOL = RTOL = 2e-2
 # DRAM bytes (read + write) the decode kernel moved per algorithmic byte in an ncu capture of the same kernel
 # at batch 16 (dram__bytes_read.sum + dram__bytes_write.sum over sum(ctx) * 2048); the kernel is a pure stream,
 # so a full launch is scaled by its tokens.
-DECODE_DRAM_PER_ALGORITHMIC_BYTE = 1.0125
+DECODE_DRAM_PER_ALGORITHMIC_BYTE = 1.0121
 
 
 def peaks():

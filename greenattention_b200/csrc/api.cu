@@ -201,6 +201,14 @@ int set_all_smem_limits() {
   return 0;
 }
 
+// Rows of a (request, kv head) pair are spread over grid.z of the combine kernel when the call has too few pairs
+// to fill the SMs (one long sequence: batch 1 x 8 kv heads would otherwise merge ~150 partials on 8 CTAs).
+unsigned combine_z(long long pairs, int rows, int sm) {
+  if (pairs >= 2LL * sm || rows <= 1) return 1;
+  const long long want = (2LL * sm + pairs - 1) / pairs;
+  return static_cast<unsigned>(want < rows ? want : rows);
+}
+
 constexpr size_t kWsHeader = 256;
 size_t ws_prefix_bytes(int batch) { return ((static_cast<size_t>(batch) + 1) * 4 + 255) / 256 * 256; }
 size_t ws_lse_bytes(int sm) { return static_cast<size_t>(2 * sm) * ga::attn::MAX_ROWS * 4; }
@@ -400,7 +408,7 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
     const int tgrid_x = d.gang ? sm / a->kv_heads * a->kv_heads : sm;
     tk->fn<<<tgrid_x, tk->threads, tk->smem, st>>>(d, kmap, vmap);
     GA_CUDA(cudaGetLastError());
-    dim3 tgrid(a->batch, a->kv_heads);
+    dim3 tgrid(a->batch, a->kv_heads, combine_z(a->batch * a->kv_heads, rows, sm));
     const int wide_mode = d.gang ? 2 : 0;
     if (a->head_dim == 128)
       GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, tgrid, dim3(128), 0, st, d, tgrid_x, d.rows_cap, ga::attn::tc::TNK, wide_mode));
@@ -409,7 +417,7 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
     g_launches = 2;
     return 0;
   }
-  dim3 cgrid(a->batch, a->kv_heads);
+  dim3 cgrid(a->batch, a->kv_heads, combine_z(a->batch * a->kv_heads, rows, sm));
   // The production decode shape (at most 8 rows per kv head, head_dim 128, 4..8 kv heads, pages of at least 32
   // tokens) gathers all kv heads of a token run per TMA box: contiguous 16 - 32 KB runs of a page stream about a
   // fifth faster than one head's 128-byte pieces. GREEN_ATTN_NO_WIDE=1 keeps such calls on the per-head kernel.

@@ -1174,7 +1174,7 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
   s.q0 = q0;
   s.slot = -1;
   if (si.cnt == 0) {
-    for (int idx = threadIdx.x; idx < rows * (HD / 4); idx += blockDim.x) {
+    for (int idx = threadIdx.x; blockIdx.z == 0 && idx < rows * (HD / 4); idx += blockDim.x) {
       int r = idx / (HD / 4), d = (idx - r * (HD / 4)) * 4;
       store_cell(p, s, HD, rows_cap, r, d, make_float4(0.f, 0.f, 0.f, 0.f), 0.f, vds);
       if (d == 0) store_lse(p, s, rows_cap, r, -INFINITY, 0.f);
@@ -1210,36 +1210,66 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
     slot_list[i] = empty ? -1 : (c == c0 ? slot0 : 2 * (c * cta_mul + cta_add));
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < rows * (HD / 4); idx += blockDim.x) {
-    int r = idx / (HD / 4), d = (idx - r * (HD / 4)) * 4;
+  // One row at a time (rows r = blockIdx.z, blockIdx.z + gridDim.z, ...: a call with few (request, kv head) pairs
+  // spreads its rows over grid.z). The 128 threads are 4 groups of 32: group pg folds the partials pg, pg + 4, ...
+  // of the row, lane `ln` the dims 4 ln .. 4 ln + 3 (+128 at head_dim 256), and the four groups are then added in a
+  // fixed order, so a unit cut into 148 slices costs 37 dependent steps instead of 148 and the result does not
+  // depend on scheduling.
+  __shared__ float red_mx[4];
+  __shared__ float red_den[4];
+  __shared__ float4 red_o[4][HD / 4];
+  const int pg = threadIdx.x >> 5, ln = threadIdx.x & 31;
+  for (int r = blockIdx.z; r < rows; r += gridDim.z) {
     float mx = -INFINITY;
-#pragma unroll 4
-    for (int i = 0; i < n_list; ++i) {
+    for (int i = threadIdx.x; i < n_list; i += 128) {
       const int slot = slot_list[i];
       if (slot >= 0) mx = fmaxf(mx, __ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + rbase + r));
     }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    if (ln == 0) red_mx[pg] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red_mx[0], red_mx[1]), fmaxf(red_mx[2], red_mx[3]));
     float den = 0.f;
-    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 o[HD / 128];
+#pragma unroll
+    for (int k = 0; k < HD / 128; ++k) o[k] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (mx != -INFINITY) {
-#pragma unroll 4
-      for (int i = 0; i < n_list; ++i) {
+#pragma unroll 2
+      for (int i = pg; i < n_list; i += 4) {
         const int slot = slot_list[i];
         if (slot < 0) continue;
-        float w = ex2(__ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + rbase + r) - mx);
-        float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (static_cast<long long>(slot) * rows_cap + rbase + r) * HD + d));
+        const long long row = static_cast<long long>(slot) * rows_cap + rbase + r;
+        const float w = ex2(__ldcg(p.ws_lse + row) - mx);
         den += w;
-        o.x += w * v.x;
-        o.y += w * v.y;
-        o.z += w * v.z;
-        o.w += w * v.w;
+#pragma unroll
+        for (int k = 0; k < HD / 128; ++k) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_o + row * HD + k * 128 + ln * 4));
+          o[k].x += w * v.x;
+          o[k].y += w * v.y;
+          o[k].z += w * v.z;
+          o[k].w += w * v.w;
+        }
       }
     }
-    float inv = den > 0.f ? 1.f / den : 0.f;
-    store_cell(p, s, HD, rows_cap, r, d, o, inv, vds);
-    if (d == 0) {
+#pragma unroll
+    for (int k = 0; k < HD / 128; ++k) red_o[pg][k * 32 + ln] = o[k];
+    if (ln == 0) red_den[pg] = den;
+    __syncthreads();
+    if (pg == 0) {
+      den = (red_den[0] + red_den[1]) + (red_den[2] + red_den[3]);
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+      for (int k = 0; k < HD / 128; ++k) {
+        const float4 a0 = red_o[0][k * 32 + ln], a1 = red_o[1][k * 32 + ln], a2 = red_o[2][k * 32 + ln], a3 = red_o[3][k * 32 + ln];
+        const float4 sum = make_float4((a0.x + a1.x) + (a2.x + a3.x), (a0.y + a1.y) + (a2.y + a3.y),
+                                       (a0.z + a1.z) + (a2.z + a3.z), (a0.w + a1.w) + (a2.w + a3.w));
+        store_cell(p, s, HD, rows_cap, r, k * 128 + ln * 4, sum, inv, vds);
+      }
       // store_lse expects (m, l) with l carrying the 2^P_SHIFT factor of the main kernel
-      store_lse(p, s, rows_cap, r, mx, den * exp2f(P_SHIFT));
+      if (ln == 0) store_lse(p, s, rows_cap, r, mx, den * exp2f(P_SHIFT));
     }
+    __syncthreads();  // the reduction buffers are reused by the next row
   }
 }
 
