@@ -402,9 +402,12 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
     const AttnInstance* tk = rep ? verify_tc_instance(a->head_dim) : extend_tc_instance(a->head_dim);
     d.tc_mode = 0;
     d.rows_cap = rep ? 32 : ga::attn::MAX_ROWS;
-    // Gangs of kv_heads CTAs walk the same pages at the same time, one kv head each (see TcWork); a few SMs stay
-    // idle when kv_heads does not divide their number, which the faster gather more than pays for.
-    d.gang = (a->kv_heads >= 2 && a->kv_heads <= 16 && sm / a->kv_heads >= 1) ? 1 : 0;
+    // GREEN_ATTN_GANG=1: gangs of kv_heads CTAs walk the same pages at the same time, one kv head each (see
+    // TcWork). The gather streams a fifth faster that way, but this kernel is bound by its per-tile softmax chain,
+    // not by the gather (measured: 257 us ganged on 144 SMs against 253 us on 148 for the B=64 verify shape), so
+    // it is off unless asked for.
+    static const bool gang_on = [] { const char* e = std::getenv("GREEN_ATTN_GANG"); return e && e[0] == '1'; }();
+    d.gang = (gang_on && a->kv_heads >= 2 && a->kv_heads <= 16 && sm / a->kv_heads >= 1) ? 1 : 0;
     const int tgrid_x = d.gang ? sm / a->kv_heads * a->kv_heads : sm;
     tk->fn<<<tgrid_x, tk->threads, tk->smem, st>>>(d, kmap, vmap);
     GA_CUDA(cudaGetLastError());

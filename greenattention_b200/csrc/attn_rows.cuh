@@ -1210,8 +1210,9 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
     slot_list[i] = empty ? -1 : (c == c0 ? slot0 : 2 * (c * cta_mul + cta_add));
   }
   __syncthreads();
-  // One row at a time (rows r = blockIdx.z, blockIdx.z + gridDim.z, ...: a call with few (request, kv head) pairs
-  // spreads its rows over grid.z). The 128 threads are 4 groups of 32: group pg folds the partials pg, pg + 4, ...
+  // Rows r = blockIdx.z, blockIdx.z + gridDim.z, ... belong to this CTA (a call with few (request, kv head) pairs
+  // spreads its rows over grid.z). A unit in many pieces (a long sequence at a small batch) goes one row at a time:
+  // the 128 threads are 4 groups of 32: group pg folds the partials pg, pg + 4, ...
   // of the row, lane `ln` the dims 4 ln .. 4 ln + 3 (+128 at head_dim 256), and the four groups are then added in a
   // fixed order, so a unit cut into 148 slices costs 37 dependent steps instead of 148 and the result does not
   // depend on scheduling.
@@ -1219,6 +1220,41 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
   __shared__ float red_den[4];
   __shared__ float4 red_o[4][HD / 4];
   const int pg = threadIdx.x >> 5, ln = threadIdx.x & 31;
+  if (n_list <= 8) {
+    // A unit in a few pieces (the usual case in a large batch): all (row, 4 dims) cells of this CTA's rows at once,
+    // each thread folding the pieces of its cells in slice order.
+    const int my_rows = (rows - static_cast<int>(blockIdx.z) + static_cast<int>(gridDim.z) - 1) / static_cast<int>(gridDim.z);
+    for (int idx = threadIdx.x; idx < my_rows * (HD / 4); idx += blockDim.x) {
+      const int r = blockIdx.z + (idx / (HD / 4)) * gridDim.z, d = (idx % (HD / 4)) * 4;
+      float mx = -INFINITY;
+#pragma unroll 4
+      for (int i = 0; i < n_list; ++i) {
+        const int slot = slot_list[i];
+        if (slot >= 0) mx = fmaxf(mx, __ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + rbase + r));
+      }
+      float den = 0.f;
+      float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (mx != -INFINITY) {
+#pragma unroll 4
+        for (int i = 0; i < n_list; ++i) {
+          const int slot = slot_list[i];
+          if (slot < 0) continue;
+          const long long row = static_cast<long long>(slot) * rows_cap + rbase + r;
+          const float w = ex2(__ldcg(p.ws_lse + row) - mx);
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_o + row * HD + d));
+          den += w;
+          o.x += w * v.x;
+          o.y += w * v.y;
+          o.z += w * v.z;
+          o.w += w * v.w;
+        }
+      }
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+      store_cell(p, s, HD, rows_cap, r, d, o, inv, vds);
+      if (d == 0) store_lse(p, s, rows_cap, r, mx, den * exp2f(P_SHIFT));  // l carries the main kernel's 2^P_SHIFT
+    }
+    return;
+  }
   for (int r = blockIdx.z; r < rows; r += gridDim.z) {
     float mx = -INFINITY;
     for (int i = threadIdx.x; i < n_list; i += 128) {

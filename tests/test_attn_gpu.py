@@ -408,3 +408,29 @@ def test_declines_out_of_scope(mutate, needle):
     mutate(kw)
     why = attn_decode.select(kw)
     assert isinstance(why, str) and needle in why, why
+
+
+def test_ganged_verify_route_in_a_fresh_process():
+    """``GREEN_ATTN_GANG=1`` (read once per process) makes the tcgen05 verify route run in gangs of kv_heads CTAs on
+    slices of whole requests; the combine kernel then looks the partial slots up by (gang, kv head). Same bar."""
+    import subprocess
+    import sys
+
+    code = (
+        "import torch, sys; sys.path.insert(0, '.');"
+        "from greenattention_b200 import attn_decode, workloads as W;"
+        "from oracle import attn_oracle;"
+        "attn_decode.ensure_ready();"
+        "cases=[W.make_paged_case([9000, 300, 5, 40000, 0, 777], [5]*6, 64, q_heads=16, kv_heads=4, head_dim=128, seed=5, descale='rand', kv_std=0.5),"
+        " W.make_paged_case([3000]*40, [16]*40, 64, q_heads=16, kv_heads=2, head_dim=256, seed=6, window=(511, 0))];\n"
+        "for c in cases:\n"
+        "    kw = W.case_to(c, 'cuda'); out, lse = attn_decode.select(kw)(**kw); torch.cuda.synchronize()\n"
+        "    ref, ref_lse = attn_oracle.paged_attention(c)\n"
+        "    assert ((out.float().cpu() - ref).abs() <= 2e-2 + 2e-2 * ref.abs()).all()\n"
+        "    fin = torch.isfinite(ref_lse); assert (lse.cpu()[fin] - ref_lse[fin]).abs().max() <= 5e-3\n"
+        "assert attn_decode.workspace_status(torch.device('cuda', 0)) == 0; print('ganged ok')"
+    )
+    env = dict(os.environ, GREEN_ATTN_GANG="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "ganged ok" in res.stdout, res.stderr[-2000:]
