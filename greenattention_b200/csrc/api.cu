@@ -120,7 +120,7 @@ const AttnInstance* decode_instance(int hd, int rows) {
   static const AttnInstance t128[5] = {make_instance<128, 1, 3, 1, 0, true, 6, 1, 2>(), make_instance<128, 1, 4, 4, 0>(),
                                        make_instance<128, 2, 3, 2, 0>(), make_instance<128, 4, 1, 4, 0>(),
                                        make_instance<128, 8, 1, 4, 0>()};
-  static const AttnInstance t256[5] = {make_instance<256, 1, 4, 2, 0, true>(), make_instance<256, 1, 4, 2, 0>(),
+  static const AttnInstance t256[5] = {make_instance<256, 1, 6, 2, 0, true>(), make_instance<256, 1, 4, 2, 0>(),
                                        make_instance<256, 2, 2, 2, 0>(), make_instance<256, 4, 1, 2, 0>(),
                                        make_instance<256, 8, 1, 2, 0>()};
   // 17..24 rows at head_dim 128 (e.g. 5 draft tokens x 4 heads per kv head) when the batch is too small for the
@@ -199,6 +199,19 @@ int set_all_smem_limits() {
     if (set_smem(*extend_instance(hd)) || set_smem(*extend_tc_instance(hd)) || set_smem(*verify_tc_instance(hd))) return 1;
   }
   return 0;
+}
+
+// Per-head gather of the split-KV kernel: gangs of kv_heads CTAs walk the same pages at the same time, one kv head
+// each, which gives DRAM the contiguous run of a page that the all-heads boxes of attn_wide.cuh give it
+// (GREEN_ATTN_NO_GANG=1: every CTA on its own (request, kv head) units). A few CTAs are dropped when kv_heads does
+// not divide the grid. Both decode entry points apply the same rule, so they cut the work identically.
+void gang_by_kv_head(const GaAttnParams* a, ga::attn::AttnDev* d, int* grid) {
+  static const bool no_gang = [] { const char* e = std::getenv("GREEN_ATTN_NO_GANG"); return e && e[0] == '1'; }();
+  // Only the 8-row head_dim 128 instance is bound by its gather; the others are bound by their consumer warps and
+  // measured 1 - 2 % slower ganged (fewer CTAs), so they keep one CTA per (request, kv head) slice.
+  const bool stream_bound = a->head_dim == 128 && a->max_seqlen_q * (a->q_heads / a->kv_heads) <= 8;
+  d->gang = (!no_gang && stream_bound && a->kv_heads >= 2 && *grid / a->kv_heads >= 1 && a->k_stride_head < a->k_stride_tok) ? 1 : 0;
+  if (d->gang) *grid = *grid / a->kv_heads * a->kv_heads;
 }
 
 // Rows of a (request, kv head) pair are spread over grid.z of the combine kernel when the call has too few pairs
@@ -439,10 +452,12 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
     return 0;
   }
   const AttnInstance* k = decode_instance(a->head_dim, rows);
-  const int grid = sm * k->occ;
+  int grid = sm * k->occ;
+  gang_by_kv_head(a, &d, &grid);
+  const int wide_mode = d.gang ? 2 : 0;
   GA_CUDA(launch_pdl(k->fn, dim3(grid), dim3(k->threads), k->smem, st, d, kmap, vmap));
-  if (a->head_dim == 128) GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN, 0));
-  else GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN, 0));
+  if (a->head_dim == 128) GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN, wide_mode));
+  else GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN, wide_mode));
   g_launches = 2;
   return 0;
 }
@@ -477,9 +492,11 @@ int ga_attn_decode_noalloc(const GaAttnParams* a, void* stream) {
     return fail("ga_attn_decode_noalloc: batch %d exceeds the built-in scratch (%d requests); use ga_attn_decode "
                 "with a workspace", a->batch, kNoAllocMaxBatch);
   const AttnInstance* k = decode_instance(a->head_dim, rows);  // rows <= 16: a 16-row instance
-  const int grid = sm * k->occ;  // same grid as ga_attn_decode, so both entry points cut the work identically
-  if (sm > kNoAllocMaxSm || static_cast<size_t>(2 * grid) * kNoAllocRows * a->head_dim * 4 > kNoAllocOBytes ||
-      static_cast<size_t>(2 * grid) * kNoAllocRows * 4 > kNoAllocLseBytes)
+  const int full_grid = sm * k->occ;  // the scratch is checked against the full grid; ganging can only drop CTAs
+  int grid = full_grid;  // same grid and the same ganging as ga_attn_decode, so both entry points cut the work identically
+  gang_by_kv_head(a, &d, &grid);
+  if (sm > kNoAllocMaxSm || static_cast<size_t>(2 * full_grid) * kNoAllocRows * a->head_dim * 4 > kNoAllocOBytes ||
+      static_cast<size_t>(2 * full_grid) * kNoAllocRows * 4 > kNoAllocLseBytes)
     return fail("ga_attn_decode_noalloc: a grid of %d CTAs on %d SMs exceeds the built-in scratch (%d SMs)", grid, sm,
                 kNoAllocMaxSm);
   if (g_noalloc_ptr[dev] == nullptr) {
@@ -503,8 +520,8 @@ int ga_attn_decode_noalloc(const GaAttnParams* a, void* stream) {
   k->fn<<<grid, k->threads, k->smem, st>>>(d, kmap, vmap);
   GA_CUDA(cudaGetLastError());
   dim3 cgrid(a->batch, a->kv_heads);
-  if (a->head_dim == 128) ga::attn::attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(d, grid, k->rows, ga::attn::TN);
-  else ga::attn::attn_combine_kernel<256><<<cgrid, 128, 0, st>>>(d, grid, k->rows, ga::attn::TN);
+  if (a->head_dim == 128) ga::attn::attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(d, grid, k->rows, ga::attn::TN, d.gang ? 2 : 0);
+  else ga::attn::attn_combine_kernel<256><<<cgrid, 128, 0, st>>>(d, grid, k->rows, ga::attn::TN, d.gang ? 2 : 0);
   GA_CUDA(cudaGetLastError());
   g_launches = 2;
   return 0;

@@ -69,7 +69,7 @@ struct AttnDev {
   int tc_mode;       // tcgen05 kernel: 0 = slices of the tile stream (decode / verify route), 1 = extend items
   int nblk;          // tcgen05 extend: the host's upper bound on the number of query blocks
   int rows_cap;      // rows per workspace slot (row stride of ws_o / ws_lse)
-  int gang;          // tcgen05 kernel, mode 0: CTAs work in gangs of kv_heads on slices of whole requests
+  int gang;          // split-KV kernels: CTAs work in gangs of kv_heads on slices of whole requests
   // split-KV workspace
   int* status;
   int* prefix;       // [batch + 1] exclusive prefix of per-request tile counts (written by CTA 0)
@@ -225,6 +225,17 @@ struct SliceWalker {
     return true;
   }
 };
+
+// Next segment of a CTA of the split-KV kernels. In a ganged launch the walker speaks of gangs and whole requests:
+// the segment becomes this CTA's kv head and its own workspace slots.
+__device__ __forceinline__ bool walk_next(const AttnDev& p, SliceWalker& walk, Seg& s) {
+  if (!walk.next(p, s)) return false;
+  if (p.gang) {
+    s.h = blockIdx.x % p.kvh;
+    if (s.slot >= 0) s.slot = 2 * static_cast<int>(blockIdx.x) + (s.slot & 1);
+  }
+  return true;
+}
 
 // One warp writes the exclusive prefix of the per-request tile counts the combine kernel works from.
 __device__ __forceinline__ void publish_prefix(const AttnDev& p, int lane, int tile) {
@@ -717,27 +728,32 @@ __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, in
   float sc[NG][4];
 #pragma unroll
   for (int j = 0; j < NG; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+  // K fragments are fetched one 128-dim slab at a time (four 8-token groups x 64 dims per ldmatrix.x4), then the MMAs
+  // of that slab run k-step-major so that consecutive MMAs accumulate into different registers. Going slab by slab
+  // keeps the fragment registers at 32 whatever the head dim (holding both slabs of a 256-dim head spilled).
 #pragma unroll
   for (int half = 0; half < NT / 32; ++half) {
-    uint32_t kb[4][C::ATOMS * 2][4];
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {
-      const uint32_t rowaddr = k_addr + ((half * 4 + jj) * 8 + lrow) * 128;
+    for (int slab = 0; slab < C::ATOMS; ++slab) {
+      uint32_t kb[4][2][4];
 #pragma unroll
-      for (int q4 = 0; q4 < C::ATOMS * 2; ++q4) {
-        const int c = q4 * 4 + lmat;
-        ldsm_x4(rowaddr + (c >> 3) * SLABB + ((static_cast<uint32_t>(c & 7) << 4) ^ xr), kb[jj][q4][0],
-                kb[jj][q4][1], kb[jj][q4][2], kb[jj][q4][3]);
+      for (int jj = 0; jj < 4; ++jj) {
+        const uint32_t rowaddr = k_addr + slab * SLABB + ((half * 4 + jj) * 8 + lrow) * 128;
+#pragma unroll
+        for (int q2 = 0; q2 < 2; ++q2) {
+          const int c = q2 * 4 + lmat;  // 16-byte chunk of the slab
+          ldsm_x4(rowaddr + ((static_cast<uint32_t>(c) << 4) ^ xr), kb[jj][q2][0], kb[jj][q2][1], kb[jj][q2][2], kb[jj][q2][3]);
+        }
       }
-    }
 #pragma unroll
-    for (int q4 = 0; q4 < C::ATOMS * 2; ++q4) {
+      for (int q2 = 0; q2 < 2; ++q2) {
 #pragma unroll
-      for (int sub = 0; sub < 2; ++sub) {
+        for (int sub = 0; sub < 2; ++sub) {
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          mma_e4m3_16x8x32_a(sc[half * 4 + jj], qf[q4 * 2 + sub][0], 0u, qf[q4 * 2 + sub][1], 0u,
-                             kb[jj][q4][sub * 2], kb[jj][q4][sub * 2 + 1]);
+          for (int jj = 0; jj < 4; ++jj) {
+            const int ks = (slab * 2 + q2) * 2 + sub;
+            mma_e4m3_16x8x32_a(sc[half * 4 + jj], qf[ks][0], 0u, qf[ks][1], 0u, kb[jj][q2][sub * 2], kb[jj][q2][sub * 2 + 1]);
+          }
         }
       }
     }
@@ -889,7 +905,11 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
   Seg one;
   bool one_pending = false;
   if (MODE == 0) {
-    walk.init(p, blockIdx.x, gridDim.x, lane);
+    // p.gang: the CTAs work in gangs of kv_heads on slices of whole requests, CTA (gang, h) taking kv head h, so
+    // that the kv heads of a page (128-byte pieces of each token's kv_heads * 128 bytes) are fetched by
+    // neighbouring CTAs at the same time and DRAM sees the contiguous run of the page (see attn_wide.cuh)
+    if (p.gang) walk.init(p, blockIdx.x / p.kvh, gridDim.x / p.kvh, lane, TN, 1);
+    else walk.init(p, blockIdx.x, gridDim.x, lane);
     if (blockIdx.x == 0 && warp == 0) publish_prefix(p, lane, TN);
   } else {
     one_pending = extend_block(p, static_cast<int>(blockIdx.x), static_cast<int>(blockIdx.y), TN, lane, one);
@@ -909,7 +929,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
     }
     while (true) {
       if (MODE == 0) {
-        if (!walk.next(p, s)) break;
+        if (!walk_next(p, walk, s)) break;
       } else {
         if (!one_pending) break;
         s = one;
@@ -939,7 +959,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
     int pos;
     while (true) {
       if (MODE == 0) {
-        if (!walk.next(p, s)) break;
+        if (!walk_next(p, walk, s)) break;
       } else {
         if (!one_pending) break;
         s = one;
@@ -1042,7 +1062,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
   int pos[2];
   while (true) {
     if (MODE == 0) {
-      if (!walk.next(p, s)) break;
+      if (!walk_next(p, walk, s)) break;
     } else {
       if (!one_pending) break;
       s = one;
