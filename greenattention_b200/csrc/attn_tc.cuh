@@ -235,6 +235,7 @@ __device__ long long g_tc_trace[TC_TRACE_ROLES][TC_TRACE_CAP];
 // Threads: 16 softmax warps (two groups of 8), 4 producer warps, 2 MMA-issuing warps, 1 scheduler warp.
 constexpr int TC_SOFTMAX = 512;
 constexpr int TC_GROUP = 256;
+constexpr int TC_GROUP4 = 128;   // verify instance: four softmax groups of four warps
 constexpr int TC_THREADS = TC_SOFTMAX + 224;
 constexpr int SEGQ = 8;          // depth of the segment ring
 constexpr int SEG_WORDS = 10;    // b, h, q0, nq, pos0, L, t_lo, t_hi, slot, valid
@@ -327,13 +328,14 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
                  b_vempty = b_vfull + 8 * C::NKV;
   const uint32_t b_qfree = b_vempty + 8 * C::NKV, b_ofree = b_qfree + 8;
   const uint32_t b_segfull = b_ofree + 8, b_segfree = b_segfull + 8 * SEGQ;
+  const uint32_t b_mpub4 = b_segfree + 8 * SEGQ;  // verify instance: one running-max barrier per softmax group
   const int* segq = reinterpret_cast<const int*>(gen + C::SEG_OFF);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 104 + 32 * C::NKV + 16 + 16 * SEGQ);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 104 + 32 * C::NKV + 16 + 16 * SEGQ + 32);
   uint32_t* lo_flag = tmem_slot + 2;  // [group][2]: the residual term of P is wanted for the group's tile 2u + g
   __nv_bfloat16* mxbuf = reinterpret_cast<__nv_bfloat16*>(gen + C::X_OFF);  // [group][part][128], rounded up
   float* mrun = reinterpret_cast<float*>(gen + C::X_OFF + 1024);            // [group][128] running max after a tile
   float* lbuf = reinterpret_cast<float*>(gen + C::X_OFF);  // [4][128] row sums, after the last tile (overlay)
-  static_assert(104 + 32 * C::NKV + 16 + 16 * SEGQ + 8 + 16 <= C::X_OFF, "barrier block overruns the exchange buffers");
+  static_assert(104 + 32 * C::NKV + 16 + 16 * SEGQ + 32 + 8 + 16 <= C::X_OFF, "barrier block overruns the exchange buffers");
   static_assert(C::SEG_OFF + SEGQ * SEG_WORDS * 4 <= C::Q_OFF, "segment ring overruns the Q tile");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -345,14 +347,16 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       mbar_init(b_segfull + 8 * i, 1);
       mbar_init(b_segfree + 8 * i, SEG_READERS);
     }
+    constexpr int GROUP = REP ? TC_GROUP4 : TC_GROUP;  // softmax threads per tile
     for (int i = 0; i < 2; ++i) {
-      mbar_init(b_pready + 8 * i, TC_GROUP);
+      mbar_init(b_pready + 8 * i, GROUP);
       mbar_init(b_pfree + 8 * i, 1);
       mbar_init(b_mpub + 8 * i, TC_GROUP);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(b_mpub4 + 8 * i, TC_GROUP4);
     for (int i = 0; i < C::NS; ++i) {
       mbar_init(b_sfull + 8 * i, 1);
-      mbar_init(b_sfree + 8 * i, TC_GROUP);
+      mbar_init(b_sfree + 8 * i, GROUP);
     }
     for (int i = 0; i < C::NKV; ++i) {
       mbar_init(b_kfull + 8 * i, 1);
@@ -405,6 +409,51 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     return valid;
   };
   Seg cur;
+
+  // Q of segment `s`: a quarter of this thread's row, rounded to e4m3, into the swizzled A tile; then the
+  // arrival that lets the QK lane start the segment.
+  auto load_q = [&](const Seg& s) {
+    // 16-element chunks of the 128 x HD tile are dealt to the 512 threads so that the lanes of a warp read whole
+    // rows (32 contiguous bytes per lane, 2 or 4 rows per warp) instead of one 32-byte piece from each of 32 rows.
+    constexpr int NC = HD / 64;   // chunks per thread
+    constexpr int CPR = HD / 16;  // chunks per row
+    uint4 x[NC], y[NC];           // all global loads are issued before the first conversion
+#pragma unroll
+    for (int i = 0; i < NC; ++i) {
+      const int id = i * TC_SOFTMAX + tid, row = id / CPR, c = id - row * CPR;
+      const int qrow = REP ? (row & 31) : row;
+      const int tq = qrow / p.gqa, hq = qrow - tq * p.gqa;
+      x[i] = y[i] = make_uint4(0, 0, 0, 0);
+      if (tq < s.nq) {
+        const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1 + c * 16;
+        if (p.q_bf16) {
+          const uint4* src = reinterpret_cast<const uint4*>(p.q + off * 2);
+          x[i] = src[0];
+          y[i] = src[1];
+        } else {
+          x[i] = *reinterpret_cast<const uint4*>(p.q + off);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NC; ++i) {
+      const int id = i * TC_SOFTMAX + tid, row = id / CPR, c = id - row * CPR;
+      uint4 pk = x[i];
+      if (p.q_bf16) {
+        auto cv = [](uint32_t a, uint32_t b) {
+          return pack_e4m3x4(bf16_bits_to_f32(a & 0xffffu), bf16_bits_to_f32(a >> 16), bf16_bits_to_f32(b & 0xffffu),
+                             bf16_bits_to_f32(b >> 16));
+        };
+        pk = make_uint4(cv(x[i].x, x[i].y), cv(x[i].z, x[i].w), cv(y[i].x, y[i].y), cv(y[i].z, y[i].w));
+      }
+      const uint32_t dst = sQ + (c >> 3) * SLAB + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
+                   : "memory");
+    }
+    TC_TRACE(18, 0);
+    fence_proxy_async();
+    mbar_arrive(b_q);
+  };
 
   if (warp >= 16 && warp < 20) {
     // ---------------------------------------------------------------- producers: four warps
@@ -563,6 +612,228 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       if (!more) break;
     }
     work.finish(lane);
+  } else if (REP && warp < 16) {
+    // ---------------------------------------------------------------- softmax, verify instance: four groups of 128
+    // At most 32 query rows (query tokens x GQA): the rows are replicated into all four 32-lane quarters of the Q
+    // tile, so S comes out four times and the warp of quarter qt takes key columns [32 qt, 32 qt + 32) of all 32
+    // rows, one row per lane (a warp can only read its own quarter of tensor memory, and a quarter maps to one
+    // scheduler: without the replication the whole softmax would sit on one scheduler's exp2 unit). A group is the
+    // four warps of one tile; group gq takes the tiles with running index = gq mod 4, so four tiles are in
+    // flight: a tile's chain of dependent steps (scores, row max, exchange, exp2, P) is several times longer than
+    // the time the HBM stream allows per tile, and only tiles in flight hide it. The 32 scores of a thread stay in
+    // registers from the max pass to the exp2 pass, so the score buffer goes back to the QK lane right after it is
+    // read. P rows 32..127 are zeroed once; O rows 0..31 are the result.
+    const int gq = warp >> 2, qt = warp & 3, rr = lane;
+    const bool owns_o = qt == 0;         // quarter 0 of O holds the result rows; warp (gq, 0) writes dims quarter gq
+    const int col_first = 32 * qt;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(qt * 32) << 16);
+    const uint32_t grp_bar = 2 + gq;     // named barrier of this group (128 threads)
+    const int krow = tid & 127;          // key row of a V tile this thread keeps finite past the end of a sequence
+    __nv_bfloat16* mx4 = mxbuf;          // [group][quarter][32], rounded up
+    float* mrun4 = mrun;                 // [group][32] running max after a tile
+    for (int i = tid; i < 4 * C::P_BYTES / 16; i += TC_SOFTMAX)
+      asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(sP + i * 16), "r"(0) : "memory");
+    fence_proxy_async();
+    named_bar_sync(1, TC_SOFTMAX);  // every zero is in place before any thread writes a P row
+    bool q_ready = false;
+    while (read_seg(sk++, cur, true)) {
+      const Seg& s = cur;
+      const int n_tiles = s.t_hi - s.t_lo;
+      const bool valid = rr / p.gqa < s.nq;
+      if (n_tiles <= 0) {
+        if (valid && owns_o) {
+          const int tq = rr / p.gqa, hq = rr - tq * p.gqa;
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(s.q0 + tq) * p.o_s0 +
+                               static_cast<long long>(s.h * p.gqa + hq) * p.o_s1 + gq * (HD / 4);
+          for (int c0 = 0; c0 < HD / 4; c0 += 8) *reinterpret_cast<uint4*>(dst + c0) = make_uint4(0, 0, 0, 0);
+          if (gq == 0 && p.lse != nullptr)
+            p.lse[static_cast<long long>(s.h * p.gqa + hq) * p.total_q + s.q0 + tq] = -INFINITY;
+        }
+        continue;
+      }
+      if (!q_ready) {
+        if (sq > 0) wait_or_flag(b_qfree, (sq - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        load_q(s);
+      }
+      q_ready = false;
+      const int pos = valid ? s.pos0 + rr / p.gqa : -1;
+      const int lo_key = p.window_left >= 0 ? pos - p.window_left : -(1 << 30);
+      const float sl2 = p.scale_log2 * (p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f);
+      float m_seen = -INFINITY, l = 0.f;  // l is relative to m_seen
+      const int it0 = it;
+      for (int t = (gq - it0) & 3; t < n_tiles; t += 4) {
+        const int gi = it0 + t;           // running tile index: buffers and barrier phases
+        const int pb = gi & 1, up = gi >> 1;  // P buffer of this tile and its use count
+        const int n0 = (s.t_lo + t) * TNK;
+        const int c_base = n0 + col_first;
+        const bool need_mask = (n0 + TNK > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
+        const int sb = gi % C::NS;
+        // A parity wait tells "phase j done" from "phase j - 1 still pending" only while the barrier is at most one
+        // phase behind. The tile that had this score buffer before (gi - NS) is another group's, and nothing this
+        // group has waited for so far proves that its scores exist; that group's published max does (its barrier
+        // cannot be two phases behind: the chain of max hand-overs this group joined at tile gi - 4 covers tile
+        // gi - 7). The other waits of a tile come after the max hand-over of tile gi - 1, which orders them.
+        if (gi >= C::NS) wait_or_flag(b_mpub4 + 8 * ((gi - C::NS) & 3), ((gi - C::NS) >> 2) & 1, failed, p.status, GA_ST_WAIT_FULL);
+        wait_or_flag(b_sfull + 8 * sb, (gi / C::NS) & 1, failed, p.status, GA_ST_WAIT_FULL);
+        tc_fence_after();
+        uint32_t v[32];
+        tmem_ld32(lane_base + C::S_COL + sb * 128 + col_first, v);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(b_sfree + 8 * sb);  // the scores are in registers: the buffer may take a later tile
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (need_mask) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = c_base + j;
+            const float x = (col <= pos && col >= lo_key) ? __uint_as_float(v[j]) : -INFINITY;
+            v[j] = __float_as_uint(x);
+            m4[j & 3] = fmaxf(m4[j & 3], x);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
+        }
+        float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * sl2;  // sl2 > 0; -inf stays -inf
+        mx4[(gq * 4 + qt) * 32 + rr] = __float2bfloat16_ru(mx);
+        // the running max after the tile before (another group's), and this tile's P buffer (free once the PV MMAs
+        // of the tile two before are done; the residual flag of this tile is complete by then)
+        float m_prev = -INFINITY;
+        if (gi >= 1) {
+          wait_or_flag(b_mpub4 + 8 * ((gi - 1) & 3), ((gi - 1) >> 2) & 1, failed, p.status, GA_ST_WAIT_FULL);
+          if (t >= 1) m_prev = mrun4[((gi - 1) & 3) * 32 + rr];
+        }
+        if (gi >= 2) wait_or_flag(b_pfree + 8 * pb, (up - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        const bool with_lo = t < 2 || lo_flag[pb * 2 + (up & 1)] != 0u;
+        named_bar_sync(grp_bar, TC_GROUP4);
+        mx = fmaxf(fmaxf(__bfloat162float(mx4[(gq * 4) * 32 + rr]), __bfloat162float(mx4[(gq * 4 + 1) * 32 + rr])),
+                   fmaxf(__bfloat162float(mx4[(gq * 4 + 2) * 32 + rr]), __bfloat162float(mx4[(gq * 4 + 3) * 32 + rr])));
+        float m_new = m_prev, alpha = 1.f;  // alpha: what O (relative to m_prev) is multiplied by
+        if (mx > m_prev + TC_LAZY || (m_prev == -INFINITY && mx > -INFINITY)) {
+          alpha = m_prev == -INFINITY ? 0.f : ex2(m_prev - mx);
+          m_new = mx;
+        }
+        if (qt == 0) mrun4[gq * 32 + rr] = m_new;
+        mbar_arrive(b_mpub4 + 8 * gq);
+        if (m_new != m_seen) {  // this thread's row sum is relative to the max it saw four tiles ago
+          l = m_seen == -INFINITY ? 0.f : l * ex2(m_seen - m_new);
+          m_seen = m_new;
+        }
+        const float sh = TC_SHIFT - (m_new == -INFINITY ? 0.f : m_new);
+        {
+          const uint32_t p_hi = sP + (pb * 2) * C::P_BYTES + rr * 128, p_lo = p_hi + C::P_BYTES;
+          const uint32_t chunk0 = static_cast<uint32_t>(col_first >> 4), rx = static_cast<uint32_t>(rr & 7);
+          l += with_lo ? exp_chunk32<false, true>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx)
+                       : exp_chunk32<false, false>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx);
+        }
+        // the vote for the residual term of the next tile that uses this P buffer (see the extend role)
+        if (valid && l < 32.f * 128.f) atomicOr(lo_flag + pb * 2 + ((up + 1) & 1), 1u);
+        // O in tensor memory is rescaled only when some row moved its max; needs the PV MMAs of the tile before
+        if (t >= 1 && owns_o && __any_sync(0xffffffffu, alpha != 1.f)) {
+          wait_or_flag(b_pfree + 8 * ((gi - 1) & 1), ((gi - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+          tc_fence_after();
+#pragma unroll 1
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            uint32_t w[32];
+            tmem_ld32(lane_base + C::O_COL + c0, w);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(__uint_as_float(w[j]) * alpha);
+            tmem_st32(lane_base + C::O_COL + c0, w);
+          }
+          tmem_wait_st();
+        }
+        // rows past the end of the sequence in the last tile: V must be finite where P is exactly 0
+        if (n0 + TNK > s.L) {
+          const int st = gi % C::NKV;
+          wait_or_flag(b_vfull + 8 * st, (gi / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
+          if (n0 + krow >= s.L) {
+#pragma unroll 1
+            for (int c = 0; c < C::ATOMS * 8; ++c) {
+              const uint32_t a = sV + st * C::KV_BYTES + (c >> 3) * SLAB + krow * 128 + ((c & 7) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
+            }
+          }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        mbar_arrive(b_pready + 8 * pb);
+      }
+      it = it0 + n_tiles;
+      {  // the next segment's Q tile, as soon as this thread is through its tiles
+        Seg nxt;
+        if (read_seg(sk, nxt, false) && nxt.t_hi > nxt.t_lo) {
+          wait_or_flag(b_qfree, sq & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+          load_q(nxt);
+          q_ready = true;
+        }
+      }
+      // ---- end of the segment: row sums over the 16 shares of a row (4 groups x 4 quarters), then O / l
+      named_bar_sync(1, TC_SOFTMAX);  // all tiles of all groups are through their max exchange
+      const int gi_last = it - 1;
+      const float m_fin = mrun4[(gi_last & 3) * 32 + rr];
+      if (m_seen != m_fin) l = m_seen == -INFINITY ? 0.f : l * ex2(m_seen - m_fin);
+      named_bar_sync(1, TC_SOFTMAX);  // the row sums overlay the max buffers
+      lbuf[(gq * 4 + qt) * 32 + rr] = l;
+      named_bar_sync(1, TC_SOFTMAX);
+      l = 0.f;
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4)
+        l += (lbuf[(k4 * 4) * 32 + rr] + lbuf[(k4 * 4 + 1) * 32 + rr]) + (lbuf[(k4 * 4 + 2) * 32 + rr] + lbuf[(k4 * 4 + 3) * 32 + rr]);
+      named_bar_sync(1, TC_SOFTMAX);  // the sums are read: the next segment may write the max buffers again
+      wait_or_flag(b_pfree + 8 * (gi_last & 1), (gi_last >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      tc_fence_after();
+      const bool bad = __any_sync(0xffffffffu, failed);
+      const bool partial = s.slot >= 0;
+      const int tq = rr / p.gqa, hq = rr - tq * p.gqa;
+      const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
+      const float inv = l > 0.f ? (partial ? 1.f : vds) / l : 0.f;
+      if (owns_o) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < HD / 4; c0 += 32) {
+          uint32_t w[32];
+          if (!bad) {
+            tmem_ld32(lane_base + C::O_COL + gq * (HD / 4) + c0, w);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) w[j] = 0u;
+          }
+          if (valid && partial) {
+            float* wdst = p.ws_o + (static_cast<long long>(s.slot) * p.rows_cap + rr) * HD + gq * (HD / 4) + c0;
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4)
+              *reinterpret_cast<float4*>(wdst + q4 * 4) =
+                  make_float4(__uint_as_float(w[q4 * 4]) * inv, __uint_as_float(w[q4 * 4 + 1]) * inv,
+                              __uint_as_float(w[q4 * 4 + 2]) * inv, __uint_as_float(w[q4 * 4 + 3]) * inv);
+          } else if (valid) {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(s.q0 + tq) * p.o_s0 +
+                                 static_cast<long long>(s.h * p.gqa + hq) * p.o_s1 + gq * (HD / 4) + c0;
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+              uint32_t o4[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(w[q8 * 8 + 2 * j]) * inv,
+                                                          __uint_as_float(w[q8 * 8 + 2 * j + 1]) * inv);
+                o4[j] = *reinterpret_cast<uint32_t*>(&b2);
+              }
+              *reinterpret_cast<uint4*>(dst + q8 * 8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            }
+          }
+        }
+      }
+      // O has been read: the PV lane may start the next segment's accumulation
+      tc_fence_before();
+      mbar_arrive(b_ofree);
+      if (valid && owns_o && gq == 0) {
+        const float lse2 = l > 0.f ? m_fin + lg2(l) - TC_SHIFT : -INFINITY;
+        if (partial) p.ws_lse[static_cast<long long>(s.slot) * p.rows_cap + rr] = lse2;
+        else if (p.lse != nullptr)
+          p.lse[static_cast<long long>(s.h * p.gqa + hq) * p.total_q + s.q0 + tq] = lse2 * 0.6931471805599453f;
+      }
+      ++sq;
+    }
   } else if (warp < 16) {
     // ---------------------------------------------------------------- softmax: two groups of 256 threads
     // Group g takes the tiles of parity g of the CTA's running tile count (its own S and P buffers), two threads per
@@ -579,7 +850,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     // one scheduler's exp2 unit. P rows 32..127 are zeroed once; O rows 0..31 are the result.
     const int g = tid >> 8, hf = (tid >> 7) & 1, r = tid & 127;
     const int part = g * 2 + hf;  // quarter of the head dims this thread loads of Q and stores of O
-    constexpr bool rep = REP;
+    constexpr bool rep = false;          // the verify instance has its own role above
     const int qt = warp & 3;             // lane quarter of this warp
     const int rr = rep ? (r & 31) : r;   // the query row this thread works for
     const bool owns_o = !rep || qt == 0; // this warp's lanes of O are result rows
@@ -592,50 +863,6 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       fence_proxy_async();
       named_bar_sync(1, TC_SOFTMAX);  // every zero is in place before any thread writes a P row
     }
-    // Q of segment `s`: a quarter of this thread's row, rounded to e4m3, into the swizzled A tile; then the
-    // arrival that lets the QK lane start the segment.
-    auto load_q = [&](const Seg& s) {
-      // 16-element chunks of the 128 x HD tile are dealt to the 512 threads so that the lanes of a warp read whole
-      // rows (32 contiguous bytes per lane, 2 or 4 rows per warp) instead of one 32-byte piece from each of 32 rows.
-      constexpr int NC = HD / 64;   // chunks per thread
-      constexpr int CPR = HD / 16;  // chunks per row
-      uint4 x[NC], y[NC];           // all global loads are issued before the first conversion
-#pragma unroll
-      for (int i = 0; i < NC; ++i) {
-        const int id = i * TC_SOFTMAX + tid, row = id / CPR, c = id - row * CPR;
-        const int qrow = rep ? (row & 31) : row;
-        const int tq = qrow / p.gqa, hq = qrow - tq * p.gqa;
-        x[i] = y[i] = make_uint4(0, 0, 0, 0);
-        if (tq < s.nq) {
-          const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1 + c * 16;
-          if (p.q_bf16) {
-            const uint4* src = reinterpret_cast<const uint4*>(p.q + off * 2);
-            x[i] = src[0];
-            y[i] = src[1];
-          } else {
-            x[i] = *reinterpret_cast<const uint4*>(p.q + off);
-          }
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < NC; ++i) {
-        const int id = i * TC_SOFTMAX + tid, row = id / CPR, c = id - row * CPR;
-        uint4 pk = x[i];
-        if (p.q_bf16) {
-          auto cv = [](uint32_t a, uint32_t b) {
-            return pack_e4m3x4(bf16_bits_to_f32(a & 0xffffu), bf16_bits_to_f32(a >> 16), bf16_bits_to_f32(b & 0xffffu),
-                               bf16_bits_to_f32(b >> 16));
-          };
-          pk = make_uint4(cv(x[i].x, x[i].y), cv(x[i].z, x[i].w), cv(y[i].x, y[i].y), cv(y[i].z, y[i].w));
-        }
-        const uint32_t dst = sQ + (c >> 3) * SLAB + row * 128 + (((c & 7) ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
-                     : "memory");
-      }
-      TC_TRACE(18, 0);
-      fence_proxy_async();
-      mbar_arrive(b_q);
-    };
     bool q_ready = false;  // the Q tile of `cur` was already loaded during the segment before
     while (read_seg(sk++, cur, true)) {
       const Seg& s = cur;
