@@ -560,7 +560,7 @@ def main():
                          "frac": per_gpu_gbs / hbm_gbs, "peak_kind": f"{peak_kind} copy bandwidth",
                          "frac_of_8TBps_nominal": per_gpu_gbs / 8000.0,
                          "traffic": int(nbytes * DECODE_DRAM_PER_ALGORITHMIC_BYTE),
-                         "kernel": "decode kernel of attn_rows.cuh (+ attn_combine_kernel inside the same events)"},
+                         "kernel": "attn_wide_kernel of attn_wide.cuh (+ attn_combine_kernel inside the same events)"},
         }
         # the same call, one event pair per call with the L2 flushed in between
         line["stats"] = quantiles(timed_calls(lambda: run(**call), max(args.steps, 20), flush))

@@ -159,7 +159,7 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 
 template <int HD, bool REP>
 AttnInstance make_tc_instance() {
-  return {ga::attn::tc::attn_tc_kernel<HD, REP>, ga::attn::tc::TC_THREADS, ga::attn::tc::TcCfg<HD>::SMEM_BYTES, 128, 1};
+  return {ga::attn::tc::attn_tc_kernel<HD, REP>, ga::attn::tc::TC_THREADS, ga::attn::tc::TcCfg<HD, REP>::SMEM_BYTES, 128, 1};
 }
 // tcgen05 extend kernel: 128 query rows per CTA, two softmax groups alternating over the key tiles.
 const AttnInstance* extend_tc_instance(int hd) {

@@ -112,13 +112,23 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-template <int HD>
+// Verify instance: only the first 32 rows of the A operand of the PV MMAs are query rows, and whatever rows 32..127
+// hold only reaches rows of O that nobody reads. So a P tile is 32 rows (4 KB), the MMA reads on into the tiles
+// behind it, and the P region has room for one tile (both terms) per softmax group.
+constexpr int TC_P4_BYTES = 32 * 128;
+
+template <int HD, bool REP = false>
 struct TcCfg {
   static constexpr int ATOMS = HD / 128;
   static constexpr int Q_BYTES = ATOMS * SLAB;
   static constexpr int P_BYTES = SLAB;                // one e4m3 term of P: 128 rows x 128 keys
   static constexpr int KV_BYTES = ATOMS * SLAB;       // one K (or V) tile
-  static constexpr int NKV = HD == 128 ? 4 : 2;       // ring depth of each of the K and V rings (even: see producers)
+  static constexpr int NK = HD == 128 ? 4 : 2;        // depth of the K ring
+  // Depth of the V ring. A V tile waits in its stage for the whole softmax of its keys (several thousand cycles
+  // after the K tile that came with it is done), so where shared memory allows (the verify instance, whose P tiles
+  // are small) the V ring is the deeper one: with four stages the stream of the verify call was bound by the turn-
+  // around of a V stage, not by HBM.
+  static constexpr int NV = REP ? (HD == 128 ? 7 : 3) : NK;
   // Header (barriers, row-max / row-sum exchange) first, then the 1024-byte aligned operand tiles. At head_dim
   // 256 this fills the 227 KiB of an SM exactly, so the kernel relies on the 1024-byte alignment it declares for
   // its dynamic shared memory and checks it at run time.
@@ -126,10 +136,10 @@ struct TcCfg {
   static constexpr int X_OFF = 512;                   // part maxima [2][2][128] bf16, running max [2][128] f32; row sums overlay both
   static constexpr int SEG_OFF = X_OFF + 2048;        // ring of segment descriptors written by the scheduler warp
   static constexpr int Q_OFF = 3072;
-  static constexpr int P_OFF = Q_OFF + Q_BYTES;       // [buffer 0|1][hi|lo]
-  static constexpr int K_OFF = P_OFF + 4 * P_BYTES;
-  static constexpr int V_OFF = K_OFF + NKV * KV_BYTES;
-  static constexpr int SMEM_BYTES = V_OFF + NKV * KV_BYTES;
+  static constexpr int P_OFF = Q_OFF + Q_BYTES;       // [buffer 0|1][hi|lo]; verify instance: [group][hi|lo] of 32 rows
+  static constexpr int K_OFF = P_OFF + (REP ? 8 * TC_P4_BYTES : 4 * P_BYTES);
+  static constexpr int V_OFF = K_OFF + NK * KV_BYTES;
+  static constexpr int SMEM_BYTES = V_OFF + NV * KV_BYTES;
   static constexpr int TMEM_COLS = 512;
   // Tensor memory: NS score buffers of 128 columns, then O (head_dim columns). Head dim 128 leaves room for a
   // third score buffer, so the QK MMAs of tile t + 2 need not wait for the softmax of tile t.
@@ -137,6 +147,20 @@ struct TcCfg {
   static constexpr int S_COL = 0;
   static constexpr int O_COL = NS * 128;
   static_assert(SMEM_BYTES <= SMEM_OPTIN, "shared memory");
+};
+
+// Position in a ring of N stages for the issuing lanes: the stage and the parity of its use count, kept by
+// increments (a lane's instruction stream is what bounds a tile there, and % and / by 3 or 7 are not cheap).
+template <int N>
+struct RingPos {
+  int i = 0;
+  uint32_t par = 0;
+  __device__ __forceinline__ void advance() {
+    if (++i == N) {
+      i = 0;
+      par ^= 1u;
+    }
+  }
 };
 
 // Bounded wait that never returns early from the kernel: a wait that runs out is recorded and every later
@@ -193,6 +217,31 @@ __device__ __forceinline__ float exp_chunk32(const uint32_t (&v)[N], float sl2, 
   return (l4[0] + l4[1]) + (l4[2] + l4[3]);
 }
 
+// The same pass with the result kept in registers (32 already masked scores of one row): the e4m3 words of the
+// row's two 16-byte chunks, and of the residual term when LO. Lets a thread finish its exp2 work before the P
+// buffer it will store to is free.
+template <bool LO>
+__device__ __forceinline__ float exp_regs32(const uint32_t (&v)[32], float sl2, float sh, uint32_t (&hi)[8], uint32_t (&lo)[8]) {
+  float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int q4 = 0; q4 < 8; ++q4) {
+    float e[4], h[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      e[j] = ex2(fmaf(__uint_as_float(v[q4 * 4 + j]), sl2, sh));
+      l4[j] += e[j];
+      if (LO) h[j] = __uint_as_float((__float_as_uint(e[j]) + 0x00080000u) & 0xfff00000u);
+    }
+    if (LO) {
+      hi[q4] = pack_e4m3x4(h[0], h[1], h[2], h[3]);
+      lo[q4] = pack_e4m3x4(e[0] - h[0], e[1] - h[1], e[2] - h[2], e[3] - h[3]);
+    } else {
+      hi[q4] = pack_e4m3x4(e[0], e[1], e[2], e[3]);
+    }
+  }
+  return (l4[0] + l4[1]) + (l4[2] + l4[3]);
+}
+
 // Class of the 32 key columns starting at `col0` for the 32 rows of a warp (row of this lane: visible keys are
 // [lo_key, pos], pos = -1 for a padding row): 4 = no row sees any of them, 0 = every row sees all of them, else a
 // mixed chunk with bit 0 set when some row is cut by its upper bound (the causal diagonal) and bit 1 when some row
@@ -223,23 +272,70 @@ __device__ __forceinline__ void mask_chunk32(uint32_t (&v)[32], int col0, int po
 #ifdef GA_TC_TRACE
 constexpr int TC_TRACE_ROLES = 8, TC_TRACE_CAP = 8192;
 __device__ long long g_tc_trace[TC_TRACE_ROLES][TC_TRACE_CAP];
+#ifdef GA_TC_ACC
+// Cheaper variant: per role and event kind, the summed cycles since the role's event before (words [kind]) and the
+// number of times (words [256 + kind]), by fire-and-forget reductions.
+#define TC_TRACE(kind, tile)                                                                                    \
+  do {                                                                                                          \
+    if (trc != nullptr) {                                                                                       \
+      const unsigned now_ = static_cast<unsigned>(clock());                                                    \
+      atomicAdd(reinterpret_cast<unsigned long long*>(trc) + ((kind) & 255), static_cast<unsigned long long>(now_ - static_cast<unsigned>(trc_n))); \
+      atomicAdd(reinterpret_cast<unsigned long long*>(trc) + 256 + ((kind) & 255), 1ull);                       \
+      trc_n = static_cast<int>(now_);                                                                           \
+    }                                                                                                           \
+  } while (0)
+#else
 #define TC_TRACE(kind, tile)                                                                                    \
   do {                                                                                                          \
     if (trc != nullptr && trc_n < TC_TRACE_CAP)                                                                 \
       trc[trc_n++] = (static_cast<long long>(((kind) << 16) | ((tile) & 0xffff)) << 40) | (clock64() & 0xffffffffffll); \
   } while (0)
+#endif
 #else
 #define TC_TRACE(kind, tile)
 #endif
+// Second optional instrument (-DGA_TC_TRACE -DGA_TC_LANEACC): the two MMA-issuing lanes sum the cycles of their
+// loop stages in registers and write the sums once, at the end, so the loop itself is not disturbed.
+#if defined(GA_TC_TRACE) && defined(GA_TC_LANEACC)
+#define LANE_ACC_DECL unsigned la_[8] = {0, 0, 0, 0, 0, 0, 0, 0}, la_t_ = static_cast<unsigned>(clock()), la_n_ = 0
+#define LANE_ACC(i)                                   \
+  do {                                                \
+    const unsigned now_ = static_cast<unsigned>(clock()); \
+    la_[i] += now_ - la_t_;                           \
+    la_t_ = now_;                                     \
+  } while (0)
+#define LANE_ACC_TILE ++la_n_
+#define LANE_ACC_DUMP(role)                                                         \
+  do {                                                                              \
+    if (blockIdx.x == 3 && lane == 0) {                                             \
+      for (int i_ = 0; i_ < 8; ++i_) g_tc_trace[role][i_] = la_[i_];                \
+      g_tc_trace[role][8] = la_n_;                                                  \
+    }                                                                               \
+  } while (0)
+#else
+#define LANE_ACC_DECL
+#define LANE_ACC(i)
+#define LANE_ACC_TILE
+#define LANE_ACC_DUMP(role)
+#endif
 
-// Threads: 16 softmax warps (two groups of 8), 4 producer warps, 2 MMA-issuing warps, 1 scheduler warp.
+// Threads: 16 softmax warps, 4 producer warps, 4 MMA-issuing warps (QK and PV x even / odd tiles), 1 scheduler warp.
 constexpr int TC_SOFTMAX = 512;
 constexpr int TC_GROUP = 256;
 constexpr int TC_GROUP4 = 128;   // verify instance: four softmax groups of four warps
-constexpr int TC_THREADS = TC_SOFTMAX + 224;
+#ifndef GA_TC_QK_LANES
+#define GA_TC_QK_LANES 1
+#endif
+#ifndef GA_TC_PV_LANES
+#define GA_TC_PV_LANES 1
+#endif
+constexpr int TC_QKL = GA_TC_QK_LANES, TC_PVL = GA_TC_PV_LANES;  // issuing lanes per MMA stream (1 or 2)
+constexpr int TC_WARP_PV2 = TC_PVL == 2 ? 23 : -1;                // warp of the second PV lane
+constexpr int TC_WARP_QK2 = TC_QKL == 2 ? (TC_PVL == 2 ? 24 : 23) : -1;
+constexpr int TC_THREADS = TC_SOFTMAX + 224 + 32 * (TC_QKL - 1) + 32 * (TC_PVL - 1);
 constexpr int SEGQ = 8;          // depth of the segment ring
 constexpr int SEG_WORDS = 10;    // b, h, q0, nq, pos0, L, t_lo, t_hi, slot, valid
-constexpr int SEG_READERS = 22;  // warps that consume every segment: 16 softmax, 4 producers, 2 issuing
+constexpr int SEG_READERS = 20 + TC_QKL + TC_PVL;  // warps that consume every segment: 16 softmax, 4 producers, the issuing ones
 
 // Work source of a persistent CTA, run by its scheduler warp (all 32 lanes call next()).
 //   mode 0 (decode / verify route): the call is one stream of 128-key tiles and contiguous slices of it go to the
@@ -306,11 +402,53 @@ struct TcWork {
 // in its last tiles and its epilogue. Two more barriers order what a segment boundary shares: `qfree` (the last
 // QK MMA of a segment has read the Q tile, committed by the QK lane) before the softmax warps overwrite Q, and
 // `ofree` (every softmax thread has read O out of tensor memory) before the PV lane starts a new accumulation.
+// Q of segment `s`: each of the 512 softmax threads takes 16-element chunks of the 128 x HD tile, rounds them to
+// e4m3 and stores them into the swizzled A tile at `sQ`.
+template <int HD, bool REP>
+__device__ __forceinline__ void load_q_body(const AttnDev& p, const Seg& s, uint32_t sQ, int tid) {
+      // 16-element chunks of the 128 x HD tile are dealt to the 512 threads so that the lanes of a warp read whole
+      // rows (32 contiguous bytes per lane, 2 or 4 rows per warp) instead of one 32-byte piece from each of 32 rows.
+      constexpr int NC = HD / 64;   // chunks per thread
+      constexpr int CPR = HD / 16;  // chunks per row
+      uint4 x[NC], y[NC];           // all global loads are issued before the first conversion
+  #pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int id = i * TC_SOFTMAX + tid, row = id / CPR, c = id - row * CPR;
+        const int qrow = REP ? (row & 31) : row;
+        const int tq = qrow / p.gqa, hq = qrow - tq * p.gqa;
+        x[i] = y[i] = make_uint4(0, 0, 0, 0);
+        if (tq < s.nq) {
+          const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1 + c * 16;
+          if (p.q_bf16) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + off * 2);
+            x[i] = src[0];
+            y[i] = src[1];
+          } else {
+            x[i] = *reinterpret_cast<const uint4*>(p.q + off);
+          }
+        }
+      }
+  #pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int id = i * TC_SOFTMAX + tid, row = id / CPR, c = id - row * CPR;
+        uint4 pk = x[i];
+        if (p.q_bf16) {
+          auto cv = [](uint32_t a, uint32_t b) {
+            return pack_e4m3x4(bf16_bits_to_f32(a & 0xffffu), bf16_bits_to_f32(a >> 16), bf16_bits_to_f32(b & 0xffffu),
+                               bf16_bits_to_f32(b >> 16));
+          };
+          pk = make_uint4(cv(x[i].x, x[i].y), cv(x[i].z, x[i].w), cv(y[i].x, y[i].y), cv(y[i].z, y[i].w));
+        }
+        const uint32_t dst = sQ + (c >> 3) * SLAB + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
+                     : "memory");
+      }
+}
 template <int HD, bool REP>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
                const __grid_constant__ CUtensorMap vmap) {
-  using C = TcCfg<HD>;
+  using C = TcCfg<HD, REP>;
   constexpr int CW = TNK / 2;          // key columns per softmax thread (two threads per row and tile)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
@@ -324,24 +462,34 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   // barrier slots; the [2] ones are indexed by tile parity = softmax group
   const uint32_t b_q = bars, b_sfull = bars + 8, b_sfree = bars + 32, b_pready = bars + 56, b_pfree = bars + 72,
                  b_mpub = bars + 88;
-  const uint32_t b_kfull = bars + 104, b_kempty = b_kfull + 8 * C::NKV, b_vfull = b_kempty + 8 * C::NKV,
-                 b_vempty = b_vfull + 8 * C::NKV;
-  const uint32_t b_qfree = b_vempty + 8 * C::NKV, b_ofree = b_qfree + 8;
+  const uint32_t b_kfull = bars + 104, b_kempty = b_kfull + 8 * C::NK, b_vfull = b_kempty + 8 * C::NK,
+                 b_vempty = b_vfull + 8 * C::NV;
+  const uint32_t b_qfree = b_vempty + 8 * C::NV, b_ofree = b_qfree + 8;
   const uint32_t b_segfull = b_ofree + 8, b_segfree = b_segfull + 8 * SEGQ;
   const uint32_t b_mpub4 = b_segfree + 8 * SEGQ;  // verify instance: one running-max barrier per softmax group
+  const uint32_t b_turn = b_mpub4 + 32;  // [2]: the PV lane of the other tile parity has issued its tile
+  const uint32_t b_turnq = b_turn + 16;  // [2]: the same for the QK lanes
+  const uint32_t b_pready4 = base + C::SEG_OFF + SEGQ * SEG_WORDS * 4;  // verify instance: one P tile per group
+  static_assert(C::SEG_OFF + SEGQ * SEG_WORDS * 4 + 32 + 8 + 16 + 48 + 16 <= C::Q_OFF, "words behind the segment ring overrun the Q tile");
   const int* segq = reinterpret_cast<const int*>(gen + C::SEG_OFF);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::BAR_OFF + 104 + 32 * C::NKV + 16 + 16 * SEGQ + 32);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + C::SEG_OFF + SEGQ * SEG_WORDS * 4 + 32);  // behind b_pready4
   uint32_t* lo_flag = tmem_slot + 2;  // [group][2]: the residual term of P is wanted for the group's tile 2u + g
+  uint32_t* lo4 = lo_flag + 4;        // verify instance, [group][3]: the same vote, from a group's tile to its next one
+  uint32_t* lo_term = lo4 + 12;       // verify instance, [group]: the group's P tile has its residual term
   __nv_bfloat16* mxbuf = reinterpret_cast<__nv_bfloat16*>(gen + C::X_OFF);  // [group][part][128], rounded up
   float* mrun = reinterpret_cast<float*>(gen + C::X_OFF + 1024);            // [group][128] running max after a tile
   float* lbuf = reinterpret_cast<float*>(gen + C::X_OFF);  // [4][128] row sums, after the last tile (overlay)
-  static_assert(104 + 32 * C::NKV + 16 + 16 * SEGQ + 32 + 8 + 16 <= C::X_OFF, "barrier block overruns the exchange buffers");
+  static_assert(104 + 16 * C::NK + 16 * C::NV + 16 + 16 * SEGQ + 32 + 32 <= C::X_OFF, "barrier block overruns the exchange buffers");
   static_assert(C::SEG_OFF + SEGQ * SEG_WORDS * 4 <= C::Q_OFF, "segment ring overruns the Q tile");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     mbar_init(b_q, TC_SOFTMAX);
-    mbar_init(b_qfree, 1);
+    mbar_init(b_qfree, TC_QKL);
+    mbar_init(b_turn, 1);
+    mbar_init(b_turn + 8, 1);
+    mbar_init(b_turnq, 1);
+    mbar_init(b_turnq + 8, 1);
     mbar_init(b_ofree, TC_SOFTMAX);
     for (int i = 0; i < SEGQ; ++i) {
       mbar_init(b_segfull + 8 * i, 1);
@@ -351,20 +499,28 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     for (int i = 0; i < 2; ++i) {
       mbar_init(b_pready + 8 * i, GROUP);
       mbar_init(b_pfree + 8 * i, 1);
-      mbar_init(b_mpub + 8 * i, TC_GROUP);
+      // verify instance: the two slots after b_pfree are P-buffer barriers too (four in turn, one per group: a
+      // group's wait then never looks at a barrier that can be two phases behind)
+      mbar_init(b_mpub + 8 * i, REP ? 1 : TC_GROUP);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(b_mpub4 + 8 * i, TC_GROUP4);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(b_mpub4 + 8 * i, TC_GROUP4);
+      mbar_init(b_pready4 + 8 * i, TC_GROUP4);
+    }
     for (int i = 0; i < C::NS; ++i) {
       mbar_init(b_sfull + 8 * i, 1);
       mbar_init(b_sfree + 8 * i, GROUP);
     }
-    for (int i = 0; i < C::NKV; ++i) {
+    for (int i = 0; i < C::NK; ++i) {
       mbar_init(b_kfull + 8 * i, 1);
       mbar_init(b_kempty + 8 * i, 1);
+    }
+    for (int i = 0; i < C::NV; ++i) {
       mbar_init(b_vfull + 8 * i, 1);
       mbar_init(b_vempty + 8 * i, 1);
     }
     lo_flag[0] = lo_flag[1] = lo_flag[2] = lo_flag[3] = 0u;
+    for (int i = 0; i < 16; ++i) lo4[i] = 0u;
     mbar_fence_init();
   }
   if (warp == 0) {
@@ -386,7 +542,10 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   long long* trc = nullptr;
   int trc_n = 0;
   if (blockIdx.x == 3) {
-    const int role = tid == 0 ? 0 : tid == 256 ? 1 : tid == 640 ? 2 : tid == 672 ? 3 : tid == 512 ? 4 : tid == 544 ? 5 : -1;
+    int role = tid == 0 ? 0 : tid == 256 ? 1 : tid == 640 ? 2 : tid == 672 ? 3 : tid == 512 ? 4 : tid == 544 ? 5 : (REP && tid == 128) ? 6 : (REP && tid == 384) ? 7 : -1;
+#ifdef GA_TC_TRACE_MASK
+    if (role >= 0 && !((GA_TC_TRACE_MASK >> role) & 1)) role = -1;
+#endif
     if (role >= 0) trc = g_tc_trace[role];
   }
 #endif
@@ -413,43 +572,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   // Q of segment `s`: a quarter of this thread's row, rounded to e4m3, into the swizzled A tile; then the
   // arrival that lets the QK lane start the segment.
   auto load_q = [&](const Seg& s) {
-    // 16-element chunks of the 128 x HD tile are dealt to the 512 threads so that the lanes of a warp read whole
-    // rows (32 contiguous bytes per lane, 2 or 4 rows per warp) instead of one 32-byte piece from each of 32 rows.
-    constexpr int NC = HD / 64;   // chunks per thread
-    constexpr int CPR = HD / 16;  // chunks per row
-    uint4 x[NC], y[NC];           // all global loads are issued before the first conversion
-#pragma unroll
-    for (int i = 0; i < NC; ++i) {
-      const int id = i * TC_SOFTMAX + tid, row = id / CPR, c = id - row * CPR;
-      const int qrow = REP ? (row & 31) : row;
-      const int tq = qrow / p.gqa, hq = qrow - tq * p.gqa;
-      x[i] = y[i] = make_uint4(0, 0, 0, 0);
-      if (tq < s.nq) {
-        const long long off = static_cast<long long>(s.q0 + tq) * p.q_s0 + static_cast<long long>(s.h * p.gqa + hq) * p.q_s1 + c * 16;
-        if (p.q_bf16) {
-          const uint4* src = reinterpret_cast<const uint4*>(p.q + off * 2);
-          x[i] = src[0];
-          y[i] = src[1];
-        } else {
-          x[i] = *reinterpret_cast<const uint4*>(p.q + off);
-        }
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < NC; ++i) {
-      const int id = i * TC_SOFTMAX + tid, row = id / CPR, c = id - row * CPR;
-      uint4 pk = x[i];
-      if (p.q_bf16) {
-        auto cv = [](uint32_t a, uint32_t b) {
-          return pack_e4m3x4(bf16_bits_to_f32(a & 0xffffu), bf16_bits_to_f32(a >> 16), bf16_bits_to_f32(b & 0xffffu),
-                             bf16_bits_to_f32(b >> 16));
-        };
-        pk = make_uint4(cv(x[i].x, x[i].y), cv(x[i].z, x[i].w), cv(y[i].x, y[i].y), cv(y[i].z, y[i].w));
-      }
-      const uint32_t dst = sQ + (c >> 3) * SLAB + row * 128 + (((c & 7) ^ (row & 7)) << 4);
-      asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(pk.x), "r"(pk.y), "r"(pk.z), "r"(pk.w)
-                   : "memory");
-    }
+    load_q_body<HD, REP>(p, s, sQ, tid);
     TC_TRACE(18, 0);
     fence_proxy_async();
     mbar_arrive(b_q);
@@ -458,8 +581,9 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   if (warp >= 16 && warp < 20) {
     // ---------------------------------------------------------------- producers: four warps
     // One warp's issue loop (barrier wait, expect_tx, page lookup, TMA issue) takes more than a thousand cycles
-    // per tile, so K and V have their own warps, and even and odd tiles too. The ring depth is even, so a stage
-    // is always refilled by the same warp (its parity waits stay within one phase).
+    // per tile, so K and V have their own warps, and even and odd tiles too. With an odd ring depth the two warps
+    // of a ring take turns on a stage; a warp's wait for a stage still never meets a barrier two phases behind,
+    // because its own tile before (two tiles back) already waited for a later MMA than the one two turns ago.
     const int pw = warp - 16, kv = pw & 1, par = pw >> 1;
     PtWindow win;
     win.b = -1;
@@ -471,7 +595,8 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       const int n_tiles = s.t_hi - s.t_lo;
       for (int t = 0; t < n_tiles && !failed; ++t, ++it) {
         if ((it & 1) != par) continue;
-        const int st = it % C::NKV, use = it / C::NKV;
+        const int depth = kv ? C::NV : C::NK;
+        const int st = it % depth, use = it / depth;
         const int n0 = (s.t_lo + t) * TNK;
         int boxes = 0;
         for (int i = 0; i < nbox; ++i) boxes += (n0 + i * p.box_tok) < s.L;
@@ -494,85 +619,158 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         TC_TRACE(41, it);
       }
     }
-  } else if (warp == 20) {
-    // ---------------------------------------------------------------- QK issue: one lane
+  } else if (warp == 20 || warp == TC_WARP_QK2) {
+    // ---------------------------------------------------------------- QK issue: one lane of each of two warps
+    // A lane's own instruction stream (barrier tests, four to eight MMAs at ~90 cycles of issue each, two commits:
+    // 1300+ cycles per tile measured in the verify call, where HBM allows a tile every 1400) bounds a tile, so
+    // each of the two MMA streams has two lanes that take the tiles of one parity each, and the lanes of a stream
+    // take turns at the issue itself: a lane issues tile t once the other has issued t - 1. Everything around the
+    // issue (barrier tests, descriptors, commits) overlaps with the other lane's turn. The order is not for the
+    // arithmetic here (the score buffers are separate accumulators) but for the waits: with three score buffers a
+    // buffer alternates between the lanes, and a lane that ran three tiles ahead of the other would meet a barrier
+    // two phases behind, which a parity wait cannot tell from one that is through.
     // The two issuing lanes (this one and the PV one) run on their own: the next scores are what a softmax group
     // waits for once it hands back its S buffer, so they must not queue behind the PV wait. Each lane's
     // instruction stream is the limit of the tensor pipe here, so descriptors are whole 64-bit registers
     // prepared before the waits, and a K step is one add.
     const uint32_t id_qk = instr_desc(TM, TNK, 0);
     const uint64_t dq = smem_desc(sQ, 16, 1024), dk = smem_desc(sK, 16, 1024);
+    RingPos<C::NK> kp;  // K stage of tile `it` and (it / NK) & 1
+    RingPos<C::NS> sp;  // score buffer of tile `it` and (it / NS) & 1
+    const int lpar = warp == TC_WARP_QK2 ? 1 : 0;  // this lane's tiles
+    LANE_ACC_DECL;
     while (read_seg(sk++, cur, true)) {
       const int n_tiles = cur.t_hi - cur.t_lo;
+      LANE_ACC(0);
       if (lane == 0 && n_tiles > 0 && !failed) {
         wait_or_flag(b_q, sq & 1, failed, p.status, GA_ST_WAIT_FULL);  // this segment's Q tile is in place
+        LANE_ACC(1);
         TC_TRACE(20, it);
-        for (int t = 0; t < n_tiles && !failed; ++t, ++it) {
-          const int st = it % C::NKV;
-          const uint64_t kb = dk + static_cast<uint64_t>(st * (C::KV_BYTES >> 4));
-          const int sb = it % C::NS;
-          const uint32_t sd = tmem + C::S_COL + sb * 128;
-          wait_or_flag(b_kfull + 8 * st, (it / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
-          TC_TRACE(21, it);
-          if (it >= C::NS) wait_or_flag(b_sfree + 8 * sb, ((it / C::NS) - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
-          if (failed) break;
+        for (int t = 0; t < n_tiles; ++t, ++it, kp.advance(), sp.advance()) {
+          if (TC_QKL == 2 && (it & 1) != lpar) continue;
+          const uint64_t kb = dk + static_cast<uint64_t>(kp.i * (C::KV_BYTES >> 4));
+          const uint32_t sd = tmem + C::S_COL + sp.i * 128;
+          const uint32_t bk = b_kfull + 8 * kp.i, bs = b_sfree + 8 * sp.i;
+          LANE_ACC(2);
+          // both barriers at once when they are through already (the common case: one shared-memory round trip)
+          if (!(mbar_test_wait(bk, kp.par) & (it < C::NS || mbar_test_wait(bs, sp.par ^ 1u)))) {
+            wait_or_flag(bk, kp.par, failed, p.status, GA_ST_WAIT_FULL);
+            LANE_ACC(3);
+            TC_TRACE(21, it);
+            if (it >= C::NS) wait_or_flag(bs, sp.par ^ 1u, failed, p.status, GA_ST_WAIT_EMPTY);
+            if (failed) break;
+          }
+          LANE_ACC(4);
           TC_TRACE(22, it);
+          if (TC_QKL == 2 && it > 0) {  // my turn: the other lane has issued the tile before
+            wait_or_flag(b_turnq + 8 * lpar, static_cast<uint32_t>((it >> 1) - 1 + lpar) & 1u, failed, p.status, GA_ST_WAIT_FULL);
+            if (failed) break;
+          }
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < HD / 32; ++ks) {
             const uint64_t off = static_cast<uint64_t>(((ks >> 2) * SLAB + (ks & 3) * 32) >> 4);
             mma_f8(sd, dq + off, kb + off, id_qk, ks > 0 ? 1 : 0);
           }
-          mma_commit(b_kempty + 8 * st);
-          mma_commit(b_sfull + 8 * sb);
+          if (TC_QKL == 2) {
+            tc_fence_before();
+            mbar_arrive(b_turnq + 8 * (lpar ^ 1));
+          }
+          LANE_ACC(5);
+          mma_commit(b_kempty + 8 * kp.i);
+          mma_commit(b_sfull + 8 * sp.i);
+          LANE_ACC(6);
+          LANE_ACC_TILE;
           TC_TRACE(23, it);
         }
-        if (!failed) mma_commit(b_qfree);  // every QK MMA of the segment has read Q
+        if (!failed) mma_commit(b_qfree);  // every QK MMA of the segment has read Q (one arrival per lane)
       }
       if (n_tiles > 0) ++sq;
       __syncwarp();
     }
-  } else if (warp == 21) {
-    // ---------------------------------------------------------------- PV issue: one lane
+    LANE_ACC_DUMP(2);
+  } else if (warp == 21 || warp == TC_WARP_PV2) {
+    // ---------------------------------------------------------------- PV issue: one lane of each of two warps
+    // The tiles of one parity each and turns at the issue, like the QK lanes. Here the order also carries the
+    // arithmetic: all PV MMAs of a segment accumulate into the same O and the softmax threads count on them running
+    // in tile order (the first overwrites O, a rescale of O sits between two of them, a tile's barrier tells that
+    // all earlier ones are done too).
     // O += P V with V as an MN-major B operand covering all head dims in one instruction (N = head_dim: at 256
     // the second 128-dim slab is found through the leading-dimension stride of the descriptor).
     const uint32_t id_pv = instr_desc(TM, HD, 1);
     const uint64_t dp = smem_desc(sP, 16, 1024), dv = smem_desc(sV, SLAB, 1024);
+    constexpr int PT = REP ? TC_P4_BYTES : C::P_BYTES;  // bytes of one term of a P tile
+    constexpr int NG = REP ? 4 : 2;                     // softmax groups = P tiles
+    const uint32_t b_pr = REP ? b_pready4 : b_pready;
+    RingPos<C::NV> vp;  // V stage of tile `it` and (it / NV) & 1
+    RingPos<NG> gp;     // softmax group of tile `it` and the parity of the group's tile count
+    const int lpar = warp == TC_WARP_PV2 ? 1 : 0;  // this lane's tiles
+    LANE_ACC_DECL;
     while (read_seg(sk++, cur, true)) {
       const int n_tiles = cur.t_hi - cur.t_lo;
+      LANE_ACC(0);
       if (lane == 0 && n_tiles > 0 && !failed) {
         // the first PV MMA of a segment overwrites O: the epilogue of the segment before must have read it
         if (sq > 0) wait_or_flag(b_ofree, (sq - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+        LANE_ACC(1);
         TC_TRACE(30, it);
-        for (int t = 0; t < n_tiles && !failed; ++t, ++it) {
-          const int st = it % C::NKV, g = it & 1;
-          const uint64_t vb = dv + static_cast<uint64_t>(st * (C::KV_BYTES >> 4));
-          const uint64_t pb = dp + static_cast<uint64_t>(g * 2 * (C::P_BYTES >> 4));
-          wait_or_flag(b_pready + 8 * g, (it >> 1) & 1, failed, p.status, GA_ST_WAIT_FULL);
-          TC_TRACE(31, it);
-          wait_or_flag(b_vfull + 8 * st, (it / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
-          if (failed) break;
+        for (int t = 0; t < n_tiles; ++t, ++it, vp.advance(), gp.advance()) {
+          if (TC_PVL == 2 && (it & 1) != lpar) continue;
+          TC_TRACE(37, it);
+          const int g = gp.i;
+          const uint64_t vb = dv + static_cast<uint64_t>(vp.i * (C::KV_BYTES >> 4));
+          const uint64_t pb = dp + static_cast<uint64_t>(g * 2 * (PT >> 4));
+          const uint32_t bp = b_pr + 8 * g, bv = b_vfull + 8 * vp.i;
+          LANE_ACC(2);
+          if (!(mbar_test_wait(bp, gp.par) & mbar_test_wait(bv, vp.par))) {  // see the QK lane
+            wait_or_flag(bp, gp.par, failed, p.status, GA_ST_WAIT_FULL);
+            LANE_ACC(3);
+            TC_TRACE(31, it);
+            wait_or_flag(bv, vp.par, failed, p.status, GA_ST_WAIT_FULL);
+            if (failed) break;
+          }
+          LANE_ACC(4);
           TC_TRACE(32, it);
           tc_fence_after();
           // residual term: always on the first tile of each group in a segment, later by the softmax threads' vote
-          const bool voted = atomicExch(lo_flag + g * 2 + ((it >> 1) & 1), 0u) != 0u;
-          const int terms = (voted || t < 2) ? 2 : 1;
+          int terms;
+          if (REP) {
+            terms = *reinterpret_cast<volatile uint32_t*>(lo_term + g) != 0u ? 2 : 1;  // written before the group's arrivals
+          } else {
+            const bool voted = atomicExch(lo_flag + g * 2 + gp.par, 0u) != 0u;
+            terms = (voted || t < 2) ? 2 : 1;
+          }
+          TC_TRACE(35, it);
+          if (TC_PVL == 2 && it > 0) {  // my turn: the other lane has issued the tile before (its n-th tile, n = it / 2 or it / 2 - 1)
+            wait_or_flag(b_turn + 8 * lpar, static_cast<uint32_t>((it >> 1) - 1 + lpar) & 1u, failed, p.status, GA_ST_WAIT_FULL);
+            if (failed) break;
+            tc_fence_after();
+          }
 #pragma unroll 1
           for (int term = 0; term < terms; ++term) {  // hi term, then the residual term while some row needs it
-            const uint64_t pa = pb + static_cast<uint64_t>(term * (C::P_BYTES >> 4));
+            const uint64_t pa = pb + static_cast<uint64_t>(term * (PT >> 4));
 #pragma unroll
             for (int ks = 0; ks < TNK / 32; ++ks)
               mma_f8(tmem + C::O_COL, pa + static_cast<uint64_t>(ks * 2), vb + static_cast<uint64_t>(ks * (32 * 128 >> 4)), id_pv,
                      (t > 0 || term > 0 || ks > 0) ? 1 : 0);
           }
-          mma_commit(b_vempty + 8 * st);
+          if (TC_PVL == 2) {
+            tc_fence_before();
+            mbar_arrive(b_turn + 8 * (lpar ^ 1));
+          }
+          TC_TRACE(36, it);
+          LANE_ACC(5);
+          mma_commit(b_vempty + 8 * vp.i);
           mma_commit(b_pfree + 8 * g);
+          LANE_ACC(6);
+          LANE_ACC_TILE;
           TC_TRACE(33 + (terms - 1), it);
         }
       }
       if (n_tiles > 0) ++sq;
       __syncwarp();
     }
+    LANE_ACC_DUMP(3);
   } else if (warp == 22) {
     // ---------------------------------------------------------------- scheduler: one warp
     // Derives this CTA's segments (device split plan / item list, with the global reads that takes) a ring's depth
@@ -622,7 +820,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     // flight: a tile's chain of dependent steps (scores, row max, exchange, exp2, P) is several times longer than
     // the time the HBM stream allows per tile, and only tiles in flight hide it. The 32 scores of a thread stay in
     // registers from the max pass to the exp2 pass, so the score buffer goes back to the QK lane right after it is
-    // read. P rows 32..127 are zeroed once; O rows 0..31 are the result.
+    // read. Each group has its own 32-row P tile (TC_P4_BYTES per term); O rows 0..31 are the result.
     const int gq = warp >> 2, qt = warp & 3, rr = lane;
     const bool owns_o = qt == 0;         // quarter 0 of O holds the result rows; warp (gq, 0) writes dims quarter gq
     const int col_first = 32 * qt;
@@ -631,15 +829,13 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     const int krow = tid & 127;          // key row of a V tile this thread keeps finite past the end of a sequence
     __nv_bfloat16* mx4 = mxbuf;          // [group][quarter][32], rounded up
     float* mrun4 = mrun;                 // [group][32] running max after a tile
-    for (int i = tid; i < 4 * C::P_BYTES / 16; i += TC_SOFTMAX)
-      asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(sP + i * 16), "r"(0) : "memory");
-    fence_proxy_async();
-    named_bar_sync(1, TC_SOFTMAX);  // every zero is in place before any thread writes a P row
     bool q_ready = false;
+    int gn = 0;  // tiles of this group so far
     while (read_seg(sk++, cur, true)) {
       const Seg& s = cur;
       const int n_tiles = s.t_hi - s.t_lo;
       const bool valid = rr / p.gqa < s.nq;
+      TC_TRACE(1, n_tiles);
       if (n_tiles <= 0) {
         if (valid && owns_o) {
           const int tq = rr / p.gqa, hq = rr - tq * p.gqa;
@@ -656,6 +852,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         load_q(s);
       }
       q_ready = false;
+      TC_TRACE(2, it);
       const int pos = valid ? s.pos0 + rr / p.gqa : -1;
       const int lo_key = p.window_left >= 0 ? pos - p.window_left : -(1 << 30);
       const float sl2 = p.scale_log2 * (p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f);
@@ -663,18 +860,19 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       const int it0 = it;
       for (int t = (gq - it0) & 3; t < n_tiles; t += 4) {
         const int gi = it0 + t;           // running tile index: buffers and barrier phases
-        const int pb = gi & 1, up = gi >> 1;  // P buffer of this tile and its use count
         const int n0 = (s.t_lo + t) * TNK;
         const int c_base = n0 + col_first;
         const bool need_mask = (n0 + TNK > s.pos0 + 1) || (p.window_left >= 0 && n0 < s.pos0 + s.nq - 1 - p.window_left);
         const int sb = gi % C::NS;
+        TC_TRACE(3, gi);
         // A parity wait tells "phase j done" from "phase j - 1 still pending" only while the barrier is at most one
         // phase behind. The tile that had this score buffer before (gi - NS) is another group's, and nothing this
         // group has waited for so far proves that its scores exist; that group's published max does (its barrier
         // cannot be two phases behind: the chain of max hand-overs this group joined at tile gi - 4 covers tile
-        // gi - 7). The other waits of a tile come after the max hand-over of tile gi - 1, which orders them.
+        // gi - 7). 
         if (gi >= C::NS) wait_or_flag(b_mpub4 + 8 * ((gi - C::NS) & 3), ((gi - C::NS) >> 2) & 1, failed, p.status, GA_ST_WAIT_FULL);
         wait_or_flag(b_sfull + 8 * sb, (gi / C::NS) & 1, failed, p.status, GA_ST_WAIT_FULL);
+        TC_TRACE(4, gi);
         tc_fence_after();
         uint32_t v[32];
         tmem_ld32(lane_base + C::S_COL + sb * 128 + col_first, v);
@@ -696,6 +894,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         }
         float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * sl2;  // sl2 > 0; -inf stays -inf
         mx4[(gq * 4 + qt) * 32 + rr] = __float2bfloat16_ru(mx);
+        TC_TRACE(5, gi);
         // the running max after the tile before (another group's), and this tile's P buffer (free once the PV MMAs
         // of the tile two before are done; the residual flag of this tile is complete by then)
         float m_prev = -INFINITY;
@@ -703,9 +902,9 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
           wait_or_flag(b_mpub4 + 8 * ((gi - 1) & 3), ((gi - 1) >> 2) & 1, failed, p.status, GA_ST_WAIT_FULL);
           if (t >= 1) m_prev = mrun4[((gi - 1) & 3) * 32 + rr];
         }
-        if (gi >= 2) wait_or_flag(b_pfree + 8 * pb, (up - 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
-        const bool with_lo = t < 2 || lo_flag[pb * 2 + (up & 1)] != 0u;
+        TC_TRACE(6, gi);
         named_bar_sync(grp_bar, TC_GROUP4);
+        TC_TRACE(7, gi);
         mx = fmaxf(fmaxf(__bfloat162float(mx4[(gq * 4) * 32 + rr]), __bfloat162float(mx4[(gq * 4 + 1) * 32 + rr])),
                    fmaxf(__bfloat162float(mx4[(gq * 4 + 2) * 32 + rr]), __bfloat162float(mx4[(gq * 4 + 3) * 32 + rr])));
         float m_new = m_prev, alpha = 1.f;  // alpha: what O (relative to m_prev) is multiplied by
@@ -720,17 +919,36 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
           m_seen = m_new;
         }
         const float sh = TC_SHIFT - (m_new == -INFINITY ? 0.f : m_new);
+        // The residual term: always on a group's first tile of a segment, later by the vote of the group's threads
+        // at its tile before (three flags per group in turn: read here, voted on below, cleared for the turn after).
+        const bool with_lo = t < 4 || lo4[gq * 3 + gn % 3] != 0u;
+        if ((tid & 127) == 0) lo4[gq * 3 + (gn + 2) % 3] = 0u;
+        uint32_t e_hi[8], e_lo[8];
+        l += with_lo ? exp_regs32<true>(v, sl2, sh, e_hi, e_lo) : exp_regs32<false>(v, sl2, sh, e_hi, e_lo);
+        if (valid && l < 32.f * 128.f) atomicOr(lo4 + gq * 3 + (gn + 1) % 3, 1u);
+        ++gn;
+        // The group's P tile is free once the PV MMAs of its own tile before are done: long ago, as a rule.
+        if (gi >= 4) wait_or_flag(b_pfree + 8 * gq, ((gi - 4) >> 2) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
         {
-          const uint32_t p_hi = sP + (pb * 2) * C::P_BYTES + rr * 128, p_lo = p_hi + C::P_BYTES;
+          const uint32_t p_hi = sP + (gq * 2) * TC_P4_BYTES + rr * 128, p_lo = p_hi + TC_P4_BYTES;
           const uint32_t chunk0 = static_cast<uint32_t>(col_first >> 4), rx = static_cast<uint32_t>(rr & 7);
-          l += with_lo ? exp_chunk32<false, true>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx)
-                       : exp_chunk32<false, false>(v, sl2, sh, c_base, pos, lo_key, p_hi, p_lo, chunk0, rx);
+#pragma unroll
+          for (int c16 = 0; c16 < 2; ++c16) {
+            const uint32_t chunk = ((chunk0 + c16) ^ rx) << 4;
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_hi + chunk), "r"(e_hi[c16 * 4]), "r"(e_hi[c16 * 4 + 1]),
+                         "r"(e_hi[c16 * 4 + 2]), "r"(e_hi[c16 * 4 + 3])
+                         : "memory");
+            if (with_lo)
+              asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(p_lo + chunk), "r"(e_lo[c16 * 4]), "r"(e_lo[c16 * 4 + 1]),
+                           "r"(e_lo[c16 * 4 + 2]), "r"(e_lo[c16 * 4 + 3])
+                           : "memory");
+          }
+          if ((tid & 127) == 0) *reinterpret_cast<volatile uint32_t*>(lo_term + gq) = with_lo ? 1u : 0u;
         }
-        // the vote for the residual term of the next tile that uses this P buffer (see the extend role)
-        if (valid && l < 32.f * 128.f) atomicOr(lo_flag + pb * 2 + ((up + 1) & 1), 1u);
+        TC_TRACE(8 + (with_lo ? 100 : 0) + (need_mask ? 50 : 0), gi);
         // O in tensor memory is rescaled only when some row moved its max; needs the PV MMAs of the tile before
         if (t >= 1 && owns_o && __any_sync(0xffffffffu, alpha != 1.f)) {
-          wait_or_flag(b_pfree + 8 * ((gi - 1) & 1), ((gi - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+          wait_or_flag(b_pfree + 8 * ((gi - 1) & 3), ((gi - 1) >> 2) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
           tc_fence_after();
 #pragma unroll 1
           for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -745,8 +963,8 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         }
         // rows past the end of the sequence in the last tile: V must be finite where P is exactly 0
         if (n0 + TNK > s.L) {
-          const int st = gi % C::NKV;
-          wait_or_flag(b_vfull + 8 * st, (gi / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
+          const int st = gi % C::NV;
+          wait_or_flag(b_vfull + 8 * st, (gi / C::NV) & 1, failed, p.status, GA_ST_WAIT_FULL);
           if (n0 + krow >= s.L) {
 #pragma unroll 1
             for (int c = 0; c < C::ATOMS * 8; ++c) {
@@ -757,9 +975,11 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         }
         fence_proxy_async();
         tc_fence_before();
-        mbar_arrive(b_pready + 8 * pb);
+        mbar_arrive(b_pready4 + 8 * gq);
+        TC_TRACE(9, gi);
       }
       it = it0 + n_tiles;
+      TC_TRACE(10, it);
       {  // the next segment's Q tile, as soon as this thread is through its tiles
         Seg nxt;
         if (read_seg(sk, nxt, false) && nxt.t_hi > nxt.t_lo) {
@@ -770,6 +990,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       }
       // ---- end of the segment: row sums over the 16 shares of a row (4 groups x 4 quarters), then O / l
       named_bar_sync(1, TC_SOFTMAX);  // all tiles of all groups are through their max exchange
+      TC_TRACE(12, it);
       const int gi_last = it - 1;
       const float m_fin = mrun4[(gi_last & 3) * 32 + rr];
       if (m_seen != m_fin) l = m_seen == -INFINITY ? 0.f : l * ex2(m_seen - m_fin);
@@ -781,7 +1002,9 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       for (int k4 = 0; k4 < 4; ++k4)
         l += (lbuf[(k4 * 4) * 32 + rr] + lbuf[(k4 * 4 + 1) * 32 + rr]) + (lbuf[(k4 * 4 + 2) * 32 + rr] + lbuf[(k4 * 4 + 3) * 32 + rr]);
       named_bar_sync(1, TC_SOFTMAX);  // the sums are read: the next segment may write the max buffers again
-      wait_or_flag(b_pfree + 8 * (gi_last & 1), (gi_last >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      TC_TRACE(11, it);
+      wait_or_flag(b_pfree + 8 * (gi_last & 3), (gi_last >> 2) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
+      TC_TRACE(13, it);
       tc_fence_after();
       const bool bad = __any_sync(0xffffffffu, failed);
       const bool partial = s.slot >= 0;
@@ -826,6 +1049,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
       // O has been read: the PV lane may start the next segment's accumulation
       tc_fence_before();
       mbar_arrive(b_ofree);
+      TC_TRACE(14, it);
       if (valid && owns_o && gq == 0) {
         const float lse2 = l > 0.f ? m_fin + lg2(l) - TC_SHIFT : -INFINITY;
         if (partial) p.ws_lse[static_cast<long long>(s.slot) * p.rows_cap + rr] = lse2;
@@ -1051,8 +1275,8 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         }
         // rows past the end of the sequence in the last tile: V must be finite where P is exactly 0
         if (n0 + TNK > s.L) {
-          const int st = gi % C::NKV;
-          wait_or_flag(b_vfull + 8 * st, (gi / C::NKV) & 1, failed, p.status, GA_ST_WAIT_FULL);
+          const int st = gi % C::NV;
+          wait_or_flag(b_vfull + 8 * st, (gi / C::NV) & 1, failed, p.status, GA_ST_WAIT_FULL);
           if (n0 + r >= s.L) {
 #pragma unroll 1
             for (int c = hf * (C::ATOMS * 4); c < (hf + 1) * (C::ATOMS * 4); ++c) {
