@@ -318,7 +318,8 @@ def bench_attn_paths(dev, hbm_gbs, bf16_tflops, flush, calls=20, check=True):
 
 def bench_long_context(dev, rank, world, steps=20, total_tokens=1 << 20, check_tokens=65536):
     """One decode step of a single sequence whose KV range is split across the ranks: local split-KV decode on the
-    shard, NCCL all-gather of the packed (O, LSE) partials, local merge. Max over ranks. Before the 1M-token
+    shard, then the exchange of the packed (O, LSE) partials and their merge, as one kernel over peer memory
+    (``kv_shard.PeerExchange``) and, beside it, as an NCCL all-gather plus a merge kernel. Max over ranks. Before the 1M-token
     timing a ``check_tokens``-token sequence goes through the same call on every rank and rank 0 compares the
     result with the oracle's attention over the whole sequence."""
     import torch.distributed as dist
@@ -341,19 +342,36 @@ def bench_long_context(dev, rank, world, steps=20, total_tokens=1 << 20, check_t
         local["cache_seqlens"] = torch.tensor([hi - lo], dtype=torch.int32, device=dev)
         return full, local
 
+    # ---- the fused exchange + merge kernel over peer memory, when the group can map it (every rank or none)
+    exch, why = None, None
+    if os.environ.get("GA_BENCH_NO_PEER_EXCHANGE") == "1":
+        why = "switched off by GA_BENCH_NO_PEER_EXCHANGE"
+    else:
+        try:
+            exch = kv_shard.PeerExchange(64, 128, dev)
+        except Exception as exc:  # noqa: BLE001 - the NCCL path is measured instead
+            why = f"{type(exc).__name__}: {exc}"[:200]
+    if not agree(exch is not None):
+        exch = None
+
     # ---- parity of the sharded path at a size the oracle handles
     parity = None
     full, local = shard_case(check_tokens, seed=12)
-    got = kv_shard.decode_kv_sharded(local)
+    got = kv_shard.decode_kv_sharded(local, exchange=exch)
+    via_nccl = kv_shard.decode_kv_sharded(local)
     torch.cuda.synchronize()
+    same = agree(bool(torch.equal(got, via_nccl)))
+    if exch is not None:
+        exch.check_status()
     if rank == 0:
         from oracle import attn_oracle
 
         ref, _ = attn_oracle.paged_attention({k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in full.items()})
         err = (got.float().cpu() - ref[0]).abs()
         parity = {"tokens": check_tokens, "ranks": world, "max_abs_err": float(err.max()),
-                  "within_atol_rtol_2e-2": bool((err <= ATOL + RTOL * ref[0].abs()).all())}
-    del full, local, got
+                  "within_atol_rtol_2e-2": bool((err <= ATOL + RTOL * ref[0].abs()).all()),
+                  "fused_exchange_equals_nccl_path_bitwise": same if exch is not None else None}
+    del full, local, got, via_nccl
     torch.cuda.empty_cache()
 
     lo, hi = kv_shard.shard_ranges(total_tokens, world, 64)[rank]
@@ -361,56 +379,77 @@ def bench_long_context(dev, rank, world, steps=20, total_tokens=1 << 20, check_t
                            kv_std=0.5, descale="rand", descale_range=(0.5, 2.0), extra_pages=8, return_lse=True)
     for name in ("q", "k_descale", "v_descale"):  # the request's query and scales are the same on every rank
         dist.broadcast(kw[name], 0)
-    for _ in range(3):
-        kv_shard.decode_kv_sharded(kw)
-    dist.barrier()
-    torch.cuda.synchronize()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
-    for _ in range(steps):
-        out = kv_shard.decode_kv_sharded(kw)
-    e.record()
-    dist.barrier()
-    torch.cuda.synchronize()
-    eager_ms = s.elapsed_time(e) / steps
-    # The step is a handful of small launches around a 33 KB exchange, so the host is its limit when it is issued
-    # call by call; a serving loop replays it from a CUDA graph (the collective is captured with it). Capture can
-    # fail on one rank only; the ranks agree on the outcome before any of them enters the replay's collectives.
-    graph_ms, graph, out_g = float("nan"), None, None
-    captured = False
-    if os.environ.get("GA_BENCH_NO_GRAPH") != "1":
-        try:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                out_g = kv_shard.decode_kv_sharded(kw)
-            captured = True
-        except Exception as exc:  # noqa: BLE001 - report the eager number only
-            print(f"long-context graph capture skipped on rank {rank}: {exc}", file=sys.stderr)
-    if agree(captured):
+
+    def time_path(exchange):
+        """(eager us, graph-replay us or None, last output) of the step, max over ranks."""
         for _ in range(3):
-            graph.replay()
+            kv_shard.decode_kv_sharded(kw, exchange=exchange)
         dist.barrier()
         torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         for _ in range(steps):
-            graph.replay()
+            out = kv_shard.decode_kv_sharded(kw, exchange=exchange)
         e.record()
         dist.barrier()
         torch.cuda.synchronize()
-        graph_ms = s.elapsed_time(e) / steps
-        if not agree(bool(torch.equal(out_g, out))):  # a replay that does not reproduce the eager result is no measurement
-            graph_ms = float("nan")
-    t = torch.tensor([eager_ms, graph_ms if graph_ms == graph_ms else -1.0], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    eager_us = t[0].item() * 1e3
-    graph_us = t[1].item() * 1e3 if t[1].item() > 0 else None  # the ranks agreed above: all replayed or none
-    us = graph_us if graph_us is not None else eager_us
-    local_bytes = (hi - lo) * 2048
-    return {"workload": f"one {total_tokens}-token sequence, KV range split over {world} GPUs, QH64/KVH8, hd128, page 64",
-            "us_per_call": us, "us_per_call_eager": eager_us, "issued_as": "cuda graph replay" if graph_us is not None else "eager calls",
-            "kv_bytes_per_gpu": local_bytes, "aggregate_tbps": total_tokens * 2048 / us / 1e6,
-            "exchange": "one NCCL all-gather of 33 KB per rank, read in place by the merge kernel",
-            "parity": parity, "finite": bool(torch.isfinite(out.float()).all())}
+        out = out.clone()
+        eager_ms = s.elapsed_time(e) / steps
+        # The step is a handful of small launches around a 33 KB exchange, so the host is its limit when it is issued
+        # call by call; a serving loop replays it from a CUDA graph (a collective is captured with it). Capture can
+        # fail on one rank only; the ranks agree on the outcome before any of them enters the replay.
+        graph_ms, graph, out_g = float("nan"), None, None
+        captured = False
+        if os.environ.get("GA_BENCH_NO_GRAPH") != "1":
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    out_g = kv_shard.decode_kv_sharded(kw, exchange=exchange)
+                captured = True
+            except Exception as exc:  # noqa: BLE001 - report the eager number only
+                print(f"long-context graph capture skipped on rank {rank}: {exc}", file=sys.stderr)
+        if agree(captured):
+            for _ in range(3):
+                graph.replay()
+            dist.barrier()
+            torch.cuda.synchronize()
+            s.record()
+            for _ in range(steps):
+                graph.replay()
+            e.record()
+            dist.barrier()
+            torch.cuda.synchronize()
+            graph_ms = s.elapsed_time(e) / steps
+            if not agree(bool(torch.equal(out_g, out))):  # a replay that does not reproduce the eager result is no measurement
+                graph_ms = float("nan")
+        t = torch.tensor([eager_ms, graph_ms if graph_ms == graph_ms else -1.0], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t[0].item() * 1e3, (t[1].item() * 1e3 if t[1].item() > 0 else None), out  # all ranks replayed or none
+
+    nccl_eager_us, nccl_graph_us, out = time_path(None)
+    nccl_us = nccl_graph_us if nccl_graph_us is not None else nccl_eager_us
+    res = {"workload": f"one {total_tokens}-token sequence, KV range split over {world} GPUs, QH64/KVH8, hd128, page 64",
+           "kv_bytes_per_gpu": (hi - lo) * 2048}
+    if exch is not None:
+        eager_us, graph_us, out_f = time_path(exch)
+        exch.check_status()
+        us = graph_us if graph_us is not None else eager_us
+        res.update({"us_per_call": us, "us_per_call_eager": eager_us,
+                    "issued_as": "cuda graph replay" if graph_us is not None else "eager calls",
+                    "exchange": "one kernel: peer stores of the 33 KB partial into every rank's buffer, flag, bounded wait, merge",
+                    "nccl_path": {"us_per_call": nccl_us, "us_per_call_eager": nccl_eager_us,
+                                  "exchange": "NCCL all-gather of 33 KB per rank + merge kernel"},
+                    "same_result_as_nccl_path": agree(bool(torch.equal(out_f, out)))})
+        out = out_f
+    else:
+        res.update({"us_per_call": nccl_us, "us_per_call_eager": nccl_eager_us,
+                    "issued_as": "cuda graph replay" if nccl_graph_us is not None else "eager calls",
+                    "exchange": "one NCCL all-gather of 33 KB per rank, read in place by the merge kernel",
+                    "fused_exchange_unavailable": why})
+    res["aggregate_tbps"] = total_tokens * 2048 / res["us_per_call"] / 1e6
+    res["parity"] = parity
+    res["finite"] = bool(torch.isfinite(out.float()).all())
+    return res
 
 
 # ------------------------------------------------------------------------------------------- main

@@ -10,13 +10,14 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib", "libgreen_attention.so")
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 EXPORTS = (
     "ga_init", "ga_attn_workspace_bytes", "ga_attn_decode", "ga_attn_extend", "ga_attn_decode_noalloc", "ga_attn_merge",
+    "ga_attn_exchange_merge",
     "ga_gdn_recurrent", "ga_gdn_verify", "ga_fp8_tensor_peak", "ga_last_launch_count", "ga_attn_workspace_status", "ga_attn_workspace_clear_status", "ga_last_error",
     "ga_abi_version", "ga_sm_count",
 )
@@ -50,6 +51,14 @@ class GaMergeParams(ctypes.Structure):
         ("o_parts", c_void_p), ("lse_parts", c_void_p), ("o_part_stride", c_int64), ("lse_part_stride", c_int64),
         ("parts", c_int32), ("rows", c_int32), ("head_dim", c_int32),
         ("out", c_void_p), ("lse", c_void_p),
+    ]
+
+
+class GaExchangeParams(ctypes.Structure):
+    _fields_ = [
+        ("mine", c_void_p), ("peer_bufs", c_void_p), ("peer_flags", c_void_p), ("epoch", c_void_p),
+        ("rank", c_int32), ("world", c_int32), ("rows", c_int32), ("head_dim", c_int32),
+        ("out", c_void_p), ("lse", c_void_p), ("status", c_void_p), ("wait_polls", c_uint32),
     ]
 
 
@@ -114,7 +123,8 @@ def lib() -> ctypes.CDLL:
         handle.ga_attn_workspace_bytes.restype = c_size_t
         for name, ptype in (("ga_attn_decode", GaAttnParams), ("ga_attn_extend", GaAttnParams),
                             ("ga_attn_decode_noalloc", GaAttnParams),
-                            ("ga_attn_merge", GaMergeParams), ("ga_gdn_recurrent", GaGdnParams),
+                            ("ga_attn_merge", GaMergeParams), ("ga_attn_exchange_merge", GaExchangeParams),
+                            ("ga_gdn_recurrent", GaGdnParams),
                             ("ga_gdn_verify", GaGdnVerifyParams)):
             fn = getattr(handle, name)
             fn.argtypes = [POINTER(ptype), c_void_p]

@@ -12,10 +12,18 @@ The reference has no multi-GPU path; its only long-context mechanism is single-G
 
 No kernel reads another GPU's memory and nothing on this path uses multicast loads. The exchange is latency
 bound, so both tensors travel in one packed buffer (one collective per call).
+
+``PeerExchange`` replaces steps 2 and 3 by ONE kernel (``ga_attn_exchange_merge``): every rank stores its partial
+into the peers' gather buffers with plain peer stores, publishes it with a flag, waits (bounded) for the peers'
+rows and merges, so the collective's launch and latency and the second kernel drop out of a step that is all
+latency. The buffers are torch symmetric memory (ordinary device memory mapped into every process of the group;
+multicast is switched off). Without it (CPU ranks, a group that cannot map peer memory) the NCCL path stays.
 """
 
 from __future__ import annotations
 
+import ctypes
+import os
 from typing import Callable, List, Optional, Tuple
 
 import torch
@@ -47,18 +55,77 @@ def unpack_partials(buf: torch.Tensor, world: int, rows: int, hd: int):
     return buf[:, : rows * hd].reshape(world, rows, hd), buf[:, rows * hd:].reshape(world, rows)
 
 
+class PeerExchange:
+    """Buffers and state of the fused exchange + merge for one (group, rows, head_dim): a gather buffer and a flag
+    array in symmetric memory, the device arrays of peer pointers, the call counter and a status word.
+    Construction is collective over ``group`` (every rank, same arguments). ``merge(mine)`` is what a decode step
+    calls; it allocates nothing and can be captured in a CUDA graph (every rank must replay the same calls)."""
+
+    STATUS_PEER_WAIT = 6
+
+    def __init__(self, rows: int, head_dim: int, device: torch.device, group: Optional[dist.ProcessGroup] = None,
+                 wait_polls: int = 0):
+        # ordinary peer mappings only: no multicast object is created for these buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.group, self.rows, self.head_dim, self.device = group, int(rows), int(head_dim), torch.device(device)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.wait_polls = int(wait_polls)
+        n = self.rows * (self.head_dim + 1)
+        self.buf = symm_mem.empty(2 * self.world * n, dtype=torch.float32, device=self.device)
+        self.flags = symm_mem.empty(2 * self.world * self.rows, dtype=torch.int32, device=self.device)
+        self.buf.zero_()
+        self.flags.zero_()
+        self._buf_hdl = symm_mem.rendezvous(self.buf, group)
+        self._flag_hdl = symm_mem.rendezvous(self.flags, group)
+        self.buf_ptrs = torch.tensor(list(self._buf_hdl.buffer_ptrs), dtype=torch.int64, device=self.device)
+        self.flag_ptrs = torch.tensor(list(self._flag_hdl.buffer_ptrs), dtype=torch.int64, device=self.device)
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.out = torch.empty((self.rows, self.head_dim), dtype=torch.bfloat16, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)  # every rank's zeros are in place before anyone stores into a peer
+
+    def merge(self, mine: torch.Tensor) -> torch.Tensor:
+        """``mine``: this rank's packed partial ``[rows * (head_dim + 1)]`` fp32. Returns the merged bf16
+        ``[rows, head_dim]`` (the same tensor every call)."""
+        from greenattention_b200 import _C
+
+        if mine.dtype != torch.float32 or mine.numel() != self.rows * (self.head_dim + 1) or not mine.is_contiguous():
+            raise ValueError("PeerExchange.merge: a dense fp32 partial of rows * (head_dim + 1) elements is expected")
+        x = _C.GaExchangeParams()
+        x.mine, x.peer_bufs, x.peer_flags = mine.data_ptr(), self.buf_ptrs.data_ptr(), self.flag_ptrs.data_ptr()
+        x.epoch, x.rank, x.world, x.rows, x.head_dim = self.epoch.data_ptr(), self.rank, self.world, self.rows, self.head_dim
+        x.out, x.lse, x.status, x.wait_polls = self.out.data_ptr(), None, self.status.data_ptr(), self.wait_polls
+        with torch.cuda.device(self.device):
+            _C.check(_C.lib().ga_attn_exchange_merge(ctypes.byref(x), torch.cuda.current_stream(self.device).cuda_stream),
+                     "ga_attn_exchange_merge")
+        return self.out
+
+    def check_status(self) -> None:
+        """Raises if a wait for a peer ran out since the last check (synchronises)."""
+        st = int(self.status.item())
+        if st:
+            self.status.zero_()
+            raise RuntimeError(f"PeerExchange: status {st} (a peer's partial did not arrive within the limit)")
+
+
 def decode_kv_sharded(
     local_kw: dict,
     group: Optional[dist.ProcessGroup] = None,
     partial_fn: Optional[Callable] = None,
     merge_fn: Optional[Callable] = None,
+    exchange: Optional[PeerExchange] = None,
 ):
     """One decode step of a KV-range-sharded sequence. ``local_kw`` is this rank's ordinary decode call over its
     own shard (batch 1, one query token, ``cache_seqlens`` = tokens held locally, 0 allowed). Returns the merged
     bf16 output ``[q_heads, head_dim]`` on every rank.
 
     ``partial_fn(**local_kw) -> (o [1, QH, HD] fp32, lse [QH, 1])`` and ``merge_fn(o_parts, lse_parts) -> out``
-    default to the CUDA entry points; tests of the exchange logic on CPU pass stand-ins.
+    default to the CUDA entry points; tests of the exchange logic on CPU pass stand-ins. With ``exchange`` (a
+    ``PeerExchange`` built for ``q_heads`` rows) the all-gather and the merge kernel are one kernel over peer memory.
     """
     default_kernels = partial_fn is None
     if partial_fn is None or merge_fn is None:
@@ -80,6 +147,8 @@ def decode_kv_sharded(
     else:
         o, lse = partial_fn(**local_kw)
         mine = pack_partial(o[0], lse[:, 0])
+    if exchange is not None and default_kernels:
+        return exchange.merge(mine)
     if world == 1:
         gathered = mine
     else:

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define GA_ABI_VERSION 2
+#define GA_ABI_VERSION 3
 
 /* Paged FP8 attention call (decode, speculative verify, extend). Mirrors the keyword arguments the
  * reference's selectors accept (green_attention/attn_decode.py:152-258). */
@@ -80,6 +80,27 @@ typedef struct GaMergeParams {
   void* out;              /* [rows, head_dim] bf16 */
   float* lse;             /* [rows] or NULL */
 } GaMergeParams;
+
+/* The same merge with the exchange of the partials inside the kernel, for one process per GPU: every rank stores
+ * its packed partial ([rows * head_dim] O then [rows] natural-log LSE, fp32) into a slot of every peer's gather
+ * buffer with peer stores, publishes it with a flag, waits (bounded) for the peers' rows and merges. `peer_bufs` and
+ * `peer_flags` are DEVICE arrays of `world` pointers: entry j is rank j's gather buffer / flag array as mapped
+ * into this process (entry `rank` is the local one). A gather buffer holds 2 * world * rows * (head_dim + 1)
+ * floats, a flag array 2 * world * rows 32-bit words, `epoch` two 32-bit words; all zeroed once, on every rank,
+ * before the first call, and used by no one else. Every rank must make the same sequence of calls. A wait that
+ * runs out (about `wait_polls` x 0.1 us; 0 = 2^23) sets *status to 6 and the call still returns.
+ * No counterpart in the reference (single GPU only). */
+typedef struct GaExchangeParams {
+  const float* mine;
+  const void* peer_bufs;
+  const void* peer_flags;
+  void* epoch;
+  int32_t rank, world, rows, head_dim;
+  void* out;              /* [rows, head_dim] bf16 */
+  float* lse;             /* [rows] or NULL */
+  int32_t* status;        /* device word, sticky */
+  uint32_t wait_polls;
+} GaExchangeParams;
 
 /* Gated-DeltaNet recurrent update over `tokens` chained tokens per request with accepted-prefix commit.
  * tokens == 1 with accept_lens == NULL is the plain decode step. */
@@ -184,6 +205,7 @@ int ga_attn_extend(const GaAttnParams* p, void* stream);
  * call is read with ga_attn_workspace_status(NULL, stream, &status). */
 int ga_attn_decode_noalloc(const GaAttnParams* p, void* stream);
 int ga_attn_merge(const GaMergeParams* p, void* stream);
+int ga_attn_exchange_merge(const GaExchangeParams* p, void* stream);
 int ga_gdn_recurrent(const GaGdnParams* p, void* stream);
 int ga_gdn_verify(const GaGdnVerifyParams* p, void* stream);
 
