@@ -33,7 +33,9 @@ from greenattention_b200 import _C, dispatch
 TILE_N = 64                # KV tokens per pipeline stage of the kernels
 SPLIT_TILE_TOKENS = 256    # plan_splits: at most one split per 256 tokens of context
 WINDOW_SPLIT_MAX_FILL = 0.4
-HEAD_DIMS = (128, 256)
+HEAD_DIMS = (128, 256, 512)
+WIDE_HEAD_DIM = 512        # four 128-byte slabs per head: decode only, at most WIDE_HEAD_ROWS rows per kv head
+WIDE_HEAD_ROWS = 8
 MAX_ROWS = 128             # GQA * query tokens per (request, kv head) a decode / verify launch can hold
 MAX_Q = dispatch.MAX_VERIFY_Q
 MAX_BATCH = int(os.environ.get("GREEN_ATTN_MAX_BATCH", "4096"))  # requests per call the workspace is sized for
@@ -284,6 +286,10 @@ def select(kw: dict) -> Union[Callable, str]:
     limit = min(MAX_Q, MAX_ROWS // (qh // kvh))
     if mq > limit:
         return f"max_seqlen_q {mq} outside 1..{limit}"
+    if hd == WIDE_HEAD_DIM and mq * (qh // kvh) > WIDE_HEAD_ROWS:
+        # the reference's (512, 8) instance takes up to 8 query tokens (attn_decode.py:58-62); here only the
+        # decode step of that shape is built
+        return f"q shape: head_dim {hd} is built for at most {WIDE_HEAD_ROWS} rows per kv head ({mq} x GQA {qh // kvh})"
     why = _paged_reason(kw)
     if why:
         return why
@@ -295,6 +301,8 @@ def select_extend(kw: dict) -> Union[Callable, str]:
     head = _common_reason(kw, "extend")
     if isinstance(head, str):
         return head
+    if head[0] == WIDE_HEAD_DIM:
+        return f"q shape: no extend kernel for head_dim {head[0]}"
     wl = head[4]
     why = _paged_reason(kw)
     if why:
@@ -366,6 +374,8 @@ def decode_noalloc(**kw):
     fn = select(kw)
     if not callable(fn):
         raise dispatch.Declined(f"decode_noalloc: {fn}")
+    if kw["q"].shape[2] == WIDE_HEAD_DIM:
+        raise dispatch.Declined(f"decode_noalloc: the built-in scratch does not hold head_dim {WIDE_HEAD_DIM} partials")
     wl = _window_left(kw)
     return _run("decode_noalloc", window_left=wl, **{k: v for k, v in kw.items() if k != "window_size"})
 

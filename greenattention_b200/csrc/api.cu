@@ -128,11 +128,20 @@ const AttnInstance* decode_instance(int hd, int rows) {
   // tcgen05 route: three warps with 8 rows each share every tile (transposed-PV path), two such sets alternate
   // over the tiles. Measured 529 us on the B=64 verify configuration against 590 us for the 32-row instance
   // (and 340 us for the tcgen05 kernel, which is why large batches go there).
+  // head_dim 512 (four 128-byte slabs per head), at most 8 rows: the transposed-PV path keeps O as 128 registers
+  // per thread, three consumer warps take a stage each of the three 64 KB stages that fit. Anything with more rows
+  // at this head dim is rejected before it gets here.
+  static const AttnInstance t512 = make_instance<512, 1, 3, 3, 0, true>();
+  if (hd == 512) return &t512;
   static const AttnInstance r24 = make_instance<128, 3, 2, 2, 0, true>();
   if (hd == 128 && rows > 16 && rows <= 24) return &r24;
   int i = rows <= 8 ? 0 : rows <= 16 ? 1 : rows <= 32 ? 2 : rows <= 64 ? 3 : 4;
   return hd == 128 ? &t128[i] : &t256[i];
 }
+// The combine kernel of a head dim, after the main kernel with programmatic stream serialization or as a plain launch.
+template <typename... Args>
+cudaError_t launch_combine(int hd, bool pdl, dim3 grid, cudaStream_t st, Args... args);
+
 const AttnInstance* extend_instance(int hd) {
   static const AttnInstance e128 = make_instance<128, 8, 1, 4, 1>();
   static const AttnInstance e256 = make_instance<256, 8, 1, 2, 1>();
@@ -156,6 +165,18 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+template <typename... Args>
+cudaError_t launch_combine(int hd, bool pdl, dim3 grid, cudaStream_t st, Args... args) {
+  auto go = [&](auto kernel) -> cudaError_t {
+    if (pdl) return launch_pdl(kernel, grid, dim3(128), 0, st, args...);
+    kernel<<<grid, 128, 0, st>>>(args...);
+    return cudaGetLastError();
+  };
+  if (hd == 128) return go(ga::attn::attn_combine_kernel<128>);
+  if (hd == 256) return go(ga::attn::attn_combine_kernel<256>);
+  return go(ga::attn::attn_combine_kernel<512>);
 }
 
 template <int HD, bool REP>
@@ -194,6 +215,7 @@ int set_smem(const AttnInstance& k) {
 int set_all_smem_limits() {
   GA_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(ga::attn::attn_wide_kernel),
                                cudaFuncAttributeMaxDynamicSharedMemorySize, ga::attn::SMEM_OPTIN));
+  if (set_smem(*decode_instance(512, 8))) return 1;
   for (int hd : {128, 256}) {
     for (int rows : {8, 16, 24, 32, 64, 128})
       if (set_smem(*decode_instance(hd, rows))) return 1;
@@ -240,8 +262,12 @@ bool pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
 // Shared validation + device-struct fill for decode and extend.
 int fill_attn(const GaAttnParams* a, ga::attn::AttnDev* d, CUtensorMap* kmap, CUtensorMap* vmap) {
   if (!a) return fail("null params");
-  if (a->head_dim != 128 && a->head_dim != 256) return fail("head_dim %d: only 128 and 256 are built", a->head_dim);
+  if (a->head_dim != 128 && a->head_dim != 256 && a->head_dim != 512)
+    return fail("head_dim %d: only 128, 256 and 512 are built", a->head_dim);
   if (a->kv_heads <= 0 || a->q_heads <= 0 || a->q_heads % a->kv_heads) return fail("q_heads %d / kv_heads %d", a->q_heads, a->kv_heads);
+  if (a->head_dim == 512 && static_cast<long long>(a->max_seqlen_q) * (a->q_heads / a->kv_heads) > 8)
+    return fail("head_dim 512: only decode with at most 8 rows per kv head is built (max_seqlen_q %d x GQA %d)",
+                a->max_seqlen_q, a->q_heads / a->kv_heads);
   if (!pow2(a->page_size)) return fail("page_size %d is not a power of two", a->page_size);
   if (a->batch <= 0) return fail("batch %d", a->batch);
   if (!a->q || !a->k_cache || !a->v_cache || !a->page_table || !a->cache_seqlens || !a->cu_seqlens_q || !a->out)
@@ -427,10 +453,7 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
     GA_CUDA(cudaGetLastError());
     dim3 tgrid(a->batch, a->kv_heads, combine_z(a->batch * a->kv_heads, rows, sm));
     const int wide_mode = d.gang ? 2 : 0;
-    if (a->head_dim == 128)
-      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, tgrid, dim3(128), 0, st, d, tgrid_x, d.rows_cap, ga::attn::tc::TNK, wide_mode));
-    else
-      GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, tgrid, dim3(128), 0, st, d, tgrid_x, d.rows_cap, ga::attn::tc::TNK, wide_mode));
+    GA_CUDA(launch_combine(a->head_dim, true, tgrid, st, d, tgrid_x, d.rows_cap, ga::attn::tc::TNK, wide_mode));
     g_launches = 2;
     return 0;
   }
@@ -457,8 +480,7 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
   gang_by_kv_head(a, &d, &grid);
   const int wide_mode = d.gang ? 2 : 0;
   GA_CUDA(launch_pdl(k->fn, dim3(grid), dim3(k->threads), k->smem, st, d, kmap, vmap));
-  if (a->head_dim == 128) GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN, wide_mode));
-  else GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<256>, cgrid, dim3(128), 0, st, d, grid, k->rows, ga::attn::TN, wide_mode));
+  GA_CUDA(launch_combine(a->head_dim, true, cgrid, st, d, grid, k->rows, ga::attn::TN, wide_mode));
   g_launches = 2;
   return 0;
 }
@@ -521,9 +543,7 @@ int ga_attn_decode_noalloc(const GaAttnParams* a, void* stream) {
   k->fn<<<grid, k->threads, k->smem, st>>>(d, kmap, vmap);
   GA_CUDA(cudaGetLastError());
   dim3 cgrid(a->batch, a->kv_heads);
-  if (a->head_dim == 128) ga::attn::attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(d, grid, k->rows, ga::attn::TN, d.gang ? 2 : 0);
-  else ga::attn::attn_combine_kernel<256><<<cgrid, 128, 0, st>>>(d, grid, k->rows, ga::attn::TN, d.gang ? 2 : 0);
-  GA_CUDA(cudaGetLastError());
+  GA_CUDA(launch_combine(a->head_dim, false, cgrid, st, d, grid, k->rows, ga::attn::TN, d.gang ? 2 : 0));
   g_launches = 2;
   return 0;
 }

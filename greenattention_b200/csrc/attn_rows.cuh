@@ -323,7 +323,7 @@ struct Cfg {
   static constexpr int NST_CAP = NST_RAW > CAP_ ? CAP_ : NST_RAW;
   static constexpr int NST = NST_CAP / LCM * LCM;
   static constexpr int SMEM_BYTES = 1024 + NST * STAGE_BYTES + MERGE_BYTES + TAIL_BYTES;
-  static_assert(HD == 128 || HD == 256, "head_dim");
+  static_assert(HD == 128 || HD == 256 || HD == 512, "head_dim");
   static_assert(NST >= 2 && NST >= LCM, "ring too shallow for this warp arrangement");
 };
 

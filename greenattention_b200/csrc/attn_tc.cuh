@@ -9,7 +9,8 @@
 //
 // A CTA works on 128 query rows at a time (128 / GQA tokens x the GQA heads of one kv head) against the keys they
 // can see, 128 keys per iteration, and is persistent: it walks a list of such segments (see TcWork) with tensor
-// memory, barriers and pipelines set up once. 22 warps:
+// memory, barriers and pipelines set up once. 23 warps:
+//   * one scheduler warp derives the CTA's segments a ring's depth ahead and publishes them in shared memory;
 //   * four producer warps (K / V x even / odd tiles) gather pages with TMA (128-byte swizzle, one box per page
 //     and 128-byte head slice, never multicast) into a K ring and a V ring;
 //   * two issuing lanes in two warps of their own: one issues S = Q K^T with both operands K-major straight from
@@ -22,6 +23,8 @@
 //     a row rests on few keys, so that a probability carries ~2^-8 relative error) into swizzled shared memory,
 //     and rescales O in tensor memory only when the running max moved by more than 1.5 in log2 (the stale max
 //     keeps P below the e4m3 limit: 2^(7 + 1.5) < 448).
+// The verify instance (REP: at most 32 query rows, replicated into the four lane quarters) has a softmax role of
+// its own: four groups of 128 threads, four tiles in flight, one 32-row P tile per group and a deeper V ring.
 // Every wait is bounded; a wait that runs out records a status word and the CTA drains to its common exit,
 // where tensor memory is released.
 #pragma once

@@ -73,6 +73,12 @@ def _peaked():
     )
 
 
+def _decode_hd512():
+    # the reference's (512, 8) instance: Gemma-4 global attention, one query token
+    return W.make_paged_case([1, 63, 300, 1025, 2500], [1] * 5, 64, q_heads=32, kv_heads=4, head_dim=512, seed=110,
+                             descale="rand", q_dtype=torch.bfloat16)
+
+
 ATTN_CASES = {
     "c1": _c1,
     "verify_ragged": _verify_ragged,
@@ -83,6 +89,7 @@ ATTN_CASES = {
     "extend_window_hd128": _extend_window_hd128,
     "saturation": _saturation,
     "peaked": _peaked,
+    "decode_hd512": _decode_hd512,
 }
 
 GDN_CASES = {

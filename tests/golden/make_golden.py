@@ -30,11 +30,13 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from tests.golden import cases  # noqa: E402
 
 
-def attention(ref_root: str) -> None:
+def attention(ref_root: str, only=None) -> None:
     sys.path[:0] = [ref_root, os.path.join(ref_root, "op_test", "sm90")]
     import test_attn_decode_fp8 as ref_tests  # the reference's test module (holds its torch oracle)
 
     for name, build in cases.ATTN_CASES.items():
+        if only and name not in only:
+            continue
         kw = build()
         out, lse = ref_tests.reference(kw)
         np.savez_compressed(
@@ -109,8 +111,10 @@ def gdn() -> None:
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="root of the GreenAttention source tree")
+    ap.add_argument("--only", nargs="*", help="attention cases to (re)generate; everything when absent")
     args = ap.parse_args()
     torch.manual_seed(0)
-    attention(args.reference)
-    host_tables(args.reference)
-    gdn()
+    attention(args.reference, args.only)
+    if not args.only:
+        host_tables(args.reference)
+        gdn()
