@@ -105,10 +105,10 @@ struct AttnInstance {
   int threads, smem, rows, occ;
 };
 
-template <int HD, int MT, int WN, int NP, int MODE, bool HALF = false, int CAP = 24, int SUB = 1, int OCC = 1>
+template <int HD, int MT, int WN, int NP, int MODE, bool HALF = false, int CAP = 24, int SUB = 1, int OCC = 1, int DS = 1>
 AttnInstance make_instance() {
-  using C = ga::attn::Cfg<HD, MT, WN, NP, CAP, SUB>;
-  return {ga::attn::attn_rows_kernel<HD, MT, WN, NP, MODE, HALF, CAP, SUB, OCC>, C::THREADS, C::SMEM_BYTES, C::ROWS,
+  using C = ga::attn::Cfg<HD, MT, WN, NP, CAP, SUB, DS>;
+  return {ga::attn::attn_rows_kernel<HD, MT, WN, NP, MODE, HALF, CAP, SUB, OCC, DS>, C::THREADS, C::SMEM_BYTES, C::ROWS,
           OCC};
 }
 
@@ -128,10 +128,10 @@ const AttnInstance* decode_instance(int hd, int rows) {
   // tcgen05 route: three warps with 8 rows each share every tile (transposed-PV path), two such sets alternate
   // over the tiles. Measured 529 us on the B=64 verify configuration against 590 us for the 32-row instance
   // (and 340 us for the tcgen05 kernel, which is why large batches go there).
-  // head_dim 512 (four 128-byte slabs per head), at most 8 rows: the transposed-PV path keeps O as 128 registers
-  // per thread, three consumer warps take a stage each of the three 64 KB stages that fit. Anything with more rows
-  // at this head dim is rejected before it gets here.
-  static const AttnInstance t512 = make_instance<512, 1, 3, 3, 0, true>();
+  // head_dim 512 (four 128-byte slabs per head), at most 8 rows: three 64 KB stages fit, a pair of warps takes each
+  // (both do the QK product of the same 8 rows, each accumulates 256 of the output dims: 64 accumulator registers
+  // per thread instead of 128, which spilled). Anything with more rows at this head dim is rejected before it gets here.
+  static const AttnInstance t512 = make_instance<512, 2, 3, 1, 0, true, 24, 1, 1, 2>();
   if (hd == 512) return &t512;
   static const AttnInstance r24 = make_instance<128, 3, 2, 2, 0, true>();
   if (hd == 128 && rows > 16 && rows <= 24) return &r24;

@@ -298,15 +298,18 @@ __device__ __forceinline__ bool extend_block(const AttnDev& p, int x_in, int h, 
 
 constexpr int gcd_(int a, int b) { return b == 0 ? a : gcd_(b, a % b); }
 
-template <int HD, int MT, int WN, int NP_ = 4, int CAP_ = 24, int SUB_ = 1>
+template <int HD, int MT, int WN, int NP_ = 4, int CAP_ = 24, int SUB_ = 1, int DS_ = 1>
 struct Cfg {
   static constexpr int ATOMS = HD / 128;
+  // 8-row path only: the DS warps that share a tile work on the SAME rows and take a 1/DS share of the output dims
+  // each (both do the whole QK product). At head_dim 512 this halves the O accumulators to 64 registers per thread.
+  static constexpr int DS = DS_;
   static constexpr int NCW = MT * WN;               // consumer warps
   // Producer warps: each issues every NP-th tile. One warp's issue loop (barrier wait, expect_tx, TMA
   // issue) takes on the order of a thousand cycles per tile, far too slow to keep HBM busy on its own.
   static constexpr int NP = NP_;
   static constexpr int THREADS = (NCW + NP) * 32;
-  static constexpr int ROWS = MT * 16;
+  static constexpr int ROWS = MT * 16 / DS_;
   static constexpr int SUB = SUB_;                               // 64-token tiles per ring stage
   static constexpr int TILE_BYTES = 2 * ATOMS * ATOM_BYTES;      // one tile: K slabs then V slabs
   static constexpr int STAGE_BYTES = SUB * TILE_BYTES;
@@ -673,11 +676,11 @@ __device__ __forceinline__ void store_lse(const AttnDev& p, const Seg& s, int ro
 // never depend on each other.
 template <class C>
 struct RowAcc8 {
-  float ot[C::ATOMS * 8][4];  // [16-dim block]: {even dim, row 2t}, {even, row 2t+1}, {odd, 2t}, {odd, 2t+1}
+  float ot[C::ATOMS * 8 / C::DS][4];  // [16-dim block]: {even dim, row 2t}, {even, row 2t+1}, {odd, 2t}, {odd, 2t+1}
   float m, l;                 // running max / sum of row g (identical in the four lanes of a quad)
   __device__ __forceinline__ void reset() {
 #pragma unroll
-    for (int i = 0; i < C::ATOMS * 8; ++i) ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f;
+    for (int i = 0; i < C::ATOMS * 8 / C::DS; ++i) ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f;
     m = -INFINITY;
     l = 0.f;
   }
@@ -717,7 +720,7 @@ __device__ __forceinline__ void load_q_frags8(const AttnDev& p, const Seg& s, in
 template <class C, int NT = TN>
 __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, int n0, uint32_t k_addr, uint32_t v_addr,
                                               const uint32_t (&qf)[C::ATOMS * 4][2], int pos, float sl2,
-                                              RowAcc8<C>& acc, int lane) {
+                                              RowAcc8<C>& acc, int lane, int dsel = 0) {
   static_assert(NT % 32 == 0, "tile length");
   constexpr int SLABB = NT * 128;  // bytes between the 128-dim slabs of a wider head
   constexpr int NG = NT / 8;       // 8-token groups
@@ -802,7 +805,7 @@ __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, in
     acc.l *= al;
     const float a0 = __shfl_sync(0xffffffffu, al, (2 * t) * 4), a1 = __shfl_sync(0xffffffffu, al, (2 * t + 1) * 4);
 #pragma unroll
-    for (int i = 0; i < C::ATOMS * 8; ++i) {
+    for (int i = 0; i < C::ATOMS * 8 / C::DS; ++i) {
       acc.ot[i][0] *= a0;
       acc.ot[i][1] *= a1;
       acc.ot[i][2] *= a0;
@@ -828,12 +831,12 @@ __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, in
     const uint32_t bl0 = pl[c2 * 4] | (pl[c2 * 4 + 1] << 16), bl1 = pl[c2 * 4 + 2] | (pl[c2 * 4 + 3] << 16);
     const uint32_t rowaddr = vbase + ((c2 * 4 + lmat) * 8 + lrow) * 128;
 #pragma unroll
-    for (int grp = 0; grp < C::ATOMS; ++grp) {  // eight 16-dim blocks at a time
+    for (int grp = 0; grp < C::ATOMS / C::DS; ++grp) {  // eight 16-dim blocks at a time; slabs of this warp's share
       uint32_t va[8][4];
 #pragma unroll
       for (int d8 = 0; d8 < 8; ++d8) {
         uint32_t r0, r1, r2, r3;
-        ldsm_x4_trans(rowaddr + grp * SLABB + ((static_cast<uint32_t>(d8) << 4) ^ xr), r0, r1, r2, r3);
+        ldsm_x4_trans(rowaddr + (dsel * (C::ATOMS / C::DS) + grp) * SLABB + ((static_cast<uint32_t>(d8) << 4) ^ xr), r0, r1, r2, r3);
         va[d8][0] = prmt(r0, r1, 0x6420);
         va[d8][1] = prmt(r0, r1, 0x7531);
         va[d8][2] = prmt(r2, r3, 0x6420);
@@ -870,11 +873,12 @@ __device__ __forceinline__ void store_pair(const AttnDev& p, const Seg& s, int h
 // MODE 0: persistent split-KV over the tile stream (decode / verify). MODE 1: one row block of
 // p.bq query tokens per CTA over everything it can see (extend). HALF: at most 8 live rows per CTA
 // (decode with GQA <= 8): rows 8..15 of the MMA tile carry no accumulators.
-template <int HD, int MT, int WN, int NP, int MODE, bool HALF, int CAP = 24, int SUB = 1, int OCC = 1>
-__global__ void __launch_bounds__(Cfg<HD, MT, WN, NP, CAP, SUB>::THREADS, OCC)
+template <int HD, int MT, int WN, int NP, int MODE, bool HALF, int CAP = 24, int SUB = 1, int OCC = 1, int DS = 1>
+__global__ void __launch_bounds__(Cfg<HD, MT, WN, NP, CAP, SUB, DS>::THREADS, OCC)
 attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap) {
-  using C = Cfg<HD, MT, WN, NP, CAP, SUB>;
+  using C = Cfg<HD, MT, WN, NP, CAP, SUB, DS>;
+  static_assert(DS == 1 || (HALF && MT == DS && C::ATOMS % DS == 0), "the dims are split between the warps that share a tile");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t ring = base;
@@ -957,6 +961,10 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
     RowAcc8<C> acc;
     uint32_t qf[C::ATOMS * 4][2];
     int pos;
+    const int dsel = DS > 1 ? mt : 0;   // share of the output dims (all warps of a tile on the same rows)
+    const int row0 = DS > 1 ? 0 : 8 * mt;  // first of this warp's 8 rows
+    constexpr int NDB = C::ATOMS * 8 / DS;  // 16-dim blocks of this warp's share
+    const int db0 = dsel * NDB;
     while (true) {
       if (MODE == 0) {
         if (!walk_next(p, walk, s)) break;
@@ -965,7 +973,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
         s = one;
         one_pending = false;
       }
-      load_q_frags8<C>(p, s, lane, qf, pos, 8 * mt);
+      load_q_frags8<C>(p, s, lane, qf, pos, row0);
       acc.reset();
       const float kds = p.kd ? p.kd[s.b * p.kd_s0 + s.h * p.kd_s1] : 1.f;
       const float vds = p.vd ? p.vd[s.b * p.vd_s0 + s.h * p.vd_s1] : 1.f;
@@ -981,7 +989,7 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
 #pragma unroll 1
         for (int u = 0; u < C::SUB && tt + u < s.t_hi; ++u)
           consume_tile8<C>(p, s, (tt + u) * TN, ring + stage * C::STAGE_BYTES + u * C::TILE_BYTES,
-                           ring + stage * C::STAGE_BYTES + u * C::TILE_BYTES + C::V_OFF, qf, pos, sl2, acc, lane);
+                           ring + stage * C::STAGE_BYTES + u * C::TILE_BYTES + C::V_OFF, qf, pos, sl2, acc, lane, dsel);
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + (C::NST + stage) * 8);
@@ -1000,13 +1008,13 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
       if (WN == 1) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int r = 8 * mt + 2 * t + e;
+          const int r = row0 + 2 * t + e;
           if (r < valid_rows) {
             const float inv = l_r[e] > 0.f ? 1.f / l_r[e] : 0.f;
 #pragma unroll
-            for (int db = 0; db < C::ATOMS * 8; ++db)
-              store_pair(p, s, HD, C::ROWS, r, db * 16 + 2 * g, acc.ot[db][e], acc.ot[db][2 + e], inv, vds);
-            if (g == 0) store_lse(p, s, C::ROWS, r, m_r[e], l_r[e]);
+            for (int db = 0; db < NDB; ++db)
+              store_pair(p, s, HD, C::ROWS, r, (db0 + db) * 16 + 2 * g, acc.ot[db][e], acc.ot[db][2 + e], inv, vds);
+            if (g == 0 && dsel == 0) store_lse(p, s, C::ROWS, r, m_r[e], l_r[e]);
           }
         }
       } else {
@@ -1014,10 +1022,12 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
           if (wn == round) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              const int r = 8 * mt + 2 * t + e;
+              const int r = row0 + 2 * t + e;
               float f_old = 0.f, f_own = 1.f, m_new = m_r[e], l_new = l_r[e];
+              // with the dims split, each share keeps its own copy of the row statistics (slots 8.. of the 16)
+              const int rs = r + 8 * dsel;
               if (round > 0) {
-                const float m_old = mergeM[r], l_old = mergeL[r];
+                const float m_old = mergeM[rs], l_old = mergeL[rs];
                 m_new = fmaxf(m_old, m_r[e]);
                 const float mu = m_new == -INFINITY ? 0.f : m_new;
                 f_old = ex2(m_old - mu);
@@ -1025,8 +1035,8 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
                 l_new = l_old * f_old + l_r[e] * f_own;
               }
 #pragma unroll
-              for (int db = 0; db < C::ATOMS * 8; ++db) {
-                float2* cell = reinterpret_cast<float2*>(mergeO + r * C::PITCH + db * 16 + 2 * g);
+              for (int db = 0; db < NDB; ++db) {
+                float2* cell = reinterpret_cast<float2*>(mergeO + r * C::PITCH + (db0 + db) * 16 + 2 * g);
                 float2 o = make_float2(acc.ot[db][e], acc.ot[db][2 + e]);
                 if (round > 0) {
                   const float2 old = *cell;
@@ -1036,8 +1046,8 @@ attn_rows_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
               }
               __syncwarp();
               if (g == 0) {
-                mergeM[r] = m_new;
-                mergeL[r] = l_new;
+                mergeM[rs] = m_new;
+                mergeL[rs] = l_new;
               }
             }
           }
