@@ -1190,15 +1190,17 @@ template <int HD>
 __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant__ AttnDev p, int G, int rows_cap,
                                                           int tile, int wide = 0) {
   const int b = blockIdx.x, h = blockIdx.y;
-  grid_dep_wait();    // the whole decode grid has finished and its partials are visible
-  grid_dep_launch();  // the next kernel in the stream may start its own prologue
+  // What only depends on the call's inputs (lengths, query offsets, scales) is read while the decode grid is still
+  // running; everything the decode grid writes (split plan, partials) comes after the wait.
   SeqInfo si = seq_info(p, b, tile);
   int ql_all = p.cu[b + 1] - p.cu[b];
-  if (ql_all <= 0) return;
   const int q0 = p.cu[b];
   const int nq = si.ql > 0 ? si.ql : (ql_all < p.max_q ? ql_all : p.max_q);
   const int rows = nq * p.gqa;
   const float vds = p.vd ? p.vd[b * p.vd_s0 + h * p.vd_s1] : 1.f;
+  grid_dep_wait();    // the whole decode grid has finished and its partials are visible
+  grid_dep_launch();  // the next kernel in the stream may start its own prologue
+  if (ql_all <= 0) return;
   Seg s;
   s.h = h;
   s.q0 = q0;
@@ -1252,31 +1254,45 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const __grid_constant
   const int pg = threadIdx.x >> 5, ln = threadIdx.x & 31;
   if (n_list <= 8) {
     // A unit in a few pieces (the usual case in a large batch): all (row, 4 dims) cells of this CTA's rows at once,
-    // each thread folding the pieces of its cells in slice order.
+    // each thread folding the pieces of its cells in slice order. The pieces' LSE go through shared memory first
+    // (one round trip for the whole CTA) and a cell's O rows are all requested before the first is used, so the
+    // kernel is two dependent round trips to the L2 however many cells a thread has (it was two per cell).
+    __shared__ float lse_few[8][MAX_ROWS];
     const int my_rows = (rows - static_cast<int>(blockIdx.z) + static_cast<int>(gridDim.z) - 1) / static_cast<int>(gridDim.z);
+    for (int idx = threadIdx.x; idx < n_list * my_rows; idx += blockDim.x) {
+      const int i = idx / my_rows, k = idx - i * my_rows;
+      const int slot = slot_list[i];
+      const int r = blockIdx.z + k * gridDim.z;
+      lse_few[i][k] = slot >= 0 ? __ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + rbase + r) : -INFINITY;
+    }
+    __syncthreads();
     for (int idx = threadIdx.x; idx < my_rows * (HD / 4); idx += blockDim.x) {
-      const int r = blockIdx.z + (idx / (HD / 4)) * gridDim.z, d = (idx % (HD / 4)) * 4;
+      const int k = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
+      const int r = blockIdx.z + k * gridDim.z;
       float mx = -INFINITY;
-#pragma unroll 4
-      for (int i = 0; i < n_list; ++i) {
-        const int slot = slot_list[i];
-        if (slot >= 0) mx = fmaxf(mx, __ldcg(p.ws_lse + static_cast<long long>(slot) * rows_cap + rbase + r));
-      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i < n_list) mx = fmaxf(mx, lse_few[i][k]);
       float den = 0.f;
       float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
       if (mx != -INFINITY) {
-#pragma unroll 4
-        for (int i = 0; i < n_list; ++i) {
-          const int slot = slot_list[i];
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int slot = i < n_list ? slot_list[i] : -1;
+          if (slot >= 0)
+            v[i] = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (static_cast<long long>(slot) * rows_cap + rbase + r) * HD + d));
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int slot = i < n_list ? slot_list[i] : -1;
           if (slot < 0) continue;
-          const long long row = static_cast<long long>(slot) * rows_cap + rbase + r;
-          const float w = ex2(__ldcg(p.ws_lse + row) - mx);
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws_o + row * HD + d));
+          const float w = ex2(lse_few[i][k] - mx);
           den += w;
-          o.x += w * v.x;
-          o.y += w * v.y;
-          o.z += w * v.z;
-          o.w += w * v.w;
+          o.x += w * v[i].x;
+          o.y += w * v[i].y;
+          o.z += w * v[i].z;
+          o.w += w * v[i].w;
         }
       }
       const float inv = den > 0.f ? 1.f / den : 0.f;
