@@ -40,6 +40,17 @@ constexpr int TNK = 128;            // keys per iteration
 constexpr int SLAB = TNK * 128;     // one 128-byte-wide swizzled slab of a 128-row tile
 constexpr float TC_SHIFT = 7.f;     // P = 2^(s - m + 7)
 constexpr float TC_LAZY = 1.5f;     // rescale O only when the row max grew by more than this (log2 units)
+// The residual term of P is kept while some thread's running share of a row sum is below this many "keys at the
+// row maximum" (P = 2^7 there). A thread's share is a lower bound of the row's sum, so past it the row rests on at
+// least that many effective keys and the e4m3 rounding of the single-term P (2^-4 relative per probability, the
+// reference's P everywhere) averages out to about 2^-4 / sqrt(3 n) of the output scale. Measured against the oracle:
+// flat rows (N(0, 0.5) keys) sit at 0.10 of the atol / rtol 2e-2 bound with 8 and at 0.05 with 32, peaked rows at 0.19
+// with either (they keep the term); 8 takes 7 % off the windowed extend, where a thread's share of a 1 024-key
+// window never reached 32.
+#ifndef GA_TC_LO_KEYS
+#define GA_TC_LO_KEYS 8
+#endif
+constexpr float TC_LO_BELOW = GA_TC_LO_KEYS * 128.f;
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   uint64_t d = 0;
@@ -928,7 +939,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         if ((tid & 127) == 0) lo4[gq * 3 + (gn + 2) % 3] = 0u;
         uint32_t e_hi[8], e_lo[8];
         l += with_lo ? exp_regs32<true>(v, sl2, sh, e_hi, e_lo) : exp_regs32<false>(v, sl2, sh, e_hi, e_lo);
-        if (valid && l < 32.f * 128.f) atomicOr(lo4 + gq * 3 + (gn + 1) % 3, 1u);
+        if (valid && l < TC_LO_BELOW) atomicOr(lo4 + gq * 3 + (gn + 1) % 3, 1u);
         ++gn;
         // The group's P tile is free once the PV MMAs of its own tile before are done: long ago, as a rule.
         if (gi >= 4) wait_or_flag(b_pfree + 8 * gq, ((gi - 4) >> 2) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
@@ -1260,7 +1271,7 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         // sum stands for at least 32 keys at the running max, the e4m3 rounding of P averages out far below the
         // tolerance. The vote is for this group's next tile (read there after the wait for this tile's PV MMAs,
         // which follow every thread's arrival below).
-        if (valid && l < 32.f * 128.f) atomicOr(lo_flag + g * 2 + ((u + 1) & 1), 1u);
+        if (valid && l < TC_LO_BELOW) atomicOr(lo_flag + g * 2 + ((u + 1) & 1), 1u);
         // O in tensor memory is rescaled only when some row of this warp moved its max; needs PV of tile t-1 done.
         if (t >= 1 && owns_o && __any_sync(0xffffffffu, alpha != 1.f)) {
           wait_or_flag(b_pfree + 8 * (g ^ 1), ((gi - 1) >> 1) & 1, failed, p.status, GA_ST_WAIT_EMPTY);
