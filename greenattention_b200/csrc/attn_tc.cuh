@@ -333,23 +333,14 @@ __device__ long long g_tc_trace[TC_TRACE_ROLES][TC_TRACE_CAP];
 #define LANE_ACC_DUMP(role)
 #endif
 
-// Threads: 16 softmax warps, 4 producer warps, 4 MMA-issuing warps (QK and PV x even / odd tiles), 1 scheduler warp.
+// Threads: 16 softmax warps, 4 producer warps, 2 MMA-issuing warps, 1 scheduler warp.
 constexpr int TC_SOFTMAX = 512;
 constexpr int TC_GROUP = 256;
 constexpr int TC_GROUP4 = 128;   // verify instance: four softmax groups of four warps
-#ifndef GA_TC_QK_LANES
-#define GA_TC_QK_LANES 1
-#endif
-#ifndef GA_TC_PV_LANES
-#define GA_TC_PV_LANES 1
-#endif
-constexpr int TC_QKL = GA_TC_QK_LANES, TC_PVL = GA_TC_PV_LANES;  // issuing lanes per MMA stream (1 or 2)
-constexpr int TC_WARP_PV2 = TC_PVL == 2 ? 23 : -1;                // warp of the second PV lane
-constexpr int TC_WARP_QK2 = TC_QKL == 2 ? (TC_PVL == 2 ? 24 : 23) : -1;
-constexpr int TC_THREADS = TC_SOFTMAX + 224 + 32 * (TC_QKL - 1) + 32 * (TC_PVL - 1);
+constexpr int TC_THREADS = TC_SOFTMAX + 224;
 constexpr int SEGQ = 8;          // depth of the segment ring
 constexpr int SEG_WORDS = 10;    // b, h, q0, nq, pos0, L, t_lo, t_hi, slot, valid
-constexpr int SEG_READERS = 20 + TC_QKL + TC_PVL;  // warps that consume every segment: 16 softmax, 4 producers, the issuing ones
+constexpr int SEG_READERS = 22;  // warps that consume every segment: 16 softmax, 4 producers, 2 issuing
 
 // Work source of a persistent CTA, run by its scheduler warp (all 32 lanes call next()).
 //   mode 0 (decode / verify route): the call is one stream of 128-key tiles and contiguous slices of it go to the
@@ -481,8 +472,6 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   const uint32_t b_qfree = b_vempty + 8 * C::NV, b_ofree = b_qfree + 8;
   const uint32_t b_segfull = b_ofree + 8, b_segfree = b_segfull + 8 * SEGQ;
   const uint32_t b_mpub4 = b_segfree + 8 * SEGQ;  // verify instance: one running-max barrier per softmax group
-  const uint32_t b_turn = b_mpub4 + 32;  // [2]: the PV lane of the other tile parity has issued its tile
-  const uint32_t b_turnq = b_turn + 16;  // [2]: the same for the QK lanes
   const uint32_t b_pready4 = base + C::SEG_OFF + SEGQ * SEG_WORDS * 4;  // verify instance: one P tile per group
   static_assert(C::SEG_OFF + SEGQ * SEG_WORDS * 4 + 32 + 8 + 16 + 48 + 16 <= C::Q_OFF, "words behind the segment ring overrun the Q tile");
   const int* segq = reinterpret_cast<const int*>(gen + C::SEG_OFF);
@@ -493,17 +482,13 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
   __nv_bfloat16* mxbuf = reinterpret_cast<__nv_bfloat16*>(gen + C::X_OFF);  // [group][part][128], rounded up
   float* mrun = reinterpret_cast<float*>(gen + C::X_OFF + 1024);            // [group][128] running max after a tile
   float* lbuf = reinterpret_cast<float*>(gen + C::X_OFF);  // [4][128] row sums, after the last tile (overlay)
-  static_assert(104 + 16 * C::NK + 16 * C::NV + 16 + 16 * SEGQ + 32 + 32 <= C::X_OFF, "barrier block overruns the exchange buffers");
+  static_assert(104 + 16 * C::NK + 16 * C::NV + 16 + 16 * SEGQ + 32 <= C::X_OFF, "barrier block overruns the exchange buffers");
   static_assert(C::SEG_OFF + SEGQ * SEG_WORDS * 4 <= C::Q_OFF, "segment ring overruns the Q tile");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     mbar_init(b_q, TC_SOFTMAX);
-    mbar_init(b_qfree, TC_QKL);
-    mbar_init(b_turn, 1);
-    mbar_init(b_turn + 8, 1);
-    mbar_init(b_turnq, 1);
-    mbar_init(b_turnq + 8, 1);
+    mbar_init(b_qfree, 1);
     mbar_init(b_ofree, TC_SOFTMAX);
     for (int i = 0; i < SEGQ; ++i) {
       mbar_init(b_segfull + 8 * i, 1);
@@ -633,25 +618,18 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         TC_TRACE(41, it);
       }
     }
-  } else if (warp == 20 || warp == TC_WARP_QK2) {
-    // ---------------------------------------------------------------- QK issue: one lane of each of two warps
-    // A lane's own instruction stream (barrier tests, four to eight MMAs at ~90 cycles of issue each, two commits:
-    // 1300+ cycles per tile measured in the verify call, where HBM allows a tile every 1400) bounds a tile, so
-    // each of the two MMA streams has two lanes that take the tiles of one parity each, and the lanes of a stream
-    // take turns at the issue itself: a lane issues tile t once the other has issued t - 1. Everything around the
-    // issue (barrier tests, descriptors, commits) overlaps with the other lane's turn. The order is not for the
-    // arithmetic here (the score buffers are separate accumulators) but for the waits: with three score buffers a
-    // buffer alternates between the lanes, and a lane that ran three tiles ahead of the other would meet a barrier
-    // two phases behind, which a parity wait cannot tell from one that is through.
+  } else if (warp == 20) {
+    // ---------------------------------------------------------------- QK issue: one lane
     // The two issuing lanes (this one and the PV one) run on their own: the next scores are what a softmax group
-    // waits for once it hands back its S buffer, so they must not queue behind the PV wait. Each lane's
-    // instruction stream is the limit of the tensor pipe here, so descriptors are whole 64-bit registers
-    // prepared before the waits, and a K step is one add.
+    // waits for once it hands back its S buffer, so they must not queue behind the PV wait. A lane's own
+    // instruction stream bounds a tile here (barrier tests, four to eight MMAs at 64 - 90 cycles of issue each, two
+    // commits), so descriptors are whole 64-bit registers prepared before the waits, ring positions are kept by
+    // increments and both barriers of a tile are tested in one round trip. (A second lane per stream, taking turns
+    // at the issue, was measured: no gain, and a 25th warp costs every thread 8 registers.)
     const uint32_t id_qk = instr_desc(TM, TNK, 0);
     const uint64_t dq = smem_desc(sQ, 16, 1024), dk = smem_desc(sK, 16, 1024);
     RingPos<C::NK> kp;  // K stage of tile `it` and (it / NK) & 1
     RingPos<C::NS> sp;  // score buffer of tile `it` and (it / NS) & 1
-    const int lpar = warp == TC_WARP_QK2 ? 1 : 0;  // this lane's tiles
     LANE_ACC_DECL;
     while (read_seg(sk++, cur, true)) {
       const int n_tiles = cur.t_hi - cur.t_lo;
@@ -661,7 +639,6 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         LANE_ACC(1);
         TC_TRACE(20, it);
         for (int t = 0; t < n_tiles; ++t, ++it, kp.advance(), sp.advance()) {
-          if (TC_QKL == 2 && (it & 1) != lpar) continue;
           const uint64_t kb = dk + static_cast<uint64_t>(kp.i * (C::KV_BYTES >> 4));
           const uint32_t sd = tmem + C::S_COL + sp.i * 128;
           const uint32_t bk = b_kfull + 8 * kp.i, bs = b_sfree + 8 * sp.i;
@@ -676,19 +653,11 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
           }
           LANE_ACC(4);
           TC_TRACE(22, it);
-          if (TC_QKL == 2 && it > 0) {  // my turn: the other lane has issued the tile before
-            wait_or_flag(b_turnq + 8 * lpar, static_cast<uint32_t>((it >> 1) - 1 + lpar) & 1u, failed, p.status, GA_ST_WAIT_FULL);
-            if (failed) break;
-          }
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < HD / 32; ++ks) {
             const uint64_t off = static_cast<uint64_t>(((ks >> 2) * SLAB + (ks & 3) * 32) >> 4);
             mma_f8(sd, dq + off, kb + off, id_qk, ks > 0 ? 1 : 0);
-          }
-          if (TC_QKL == 2) {
-            tc_fence_before();
-            mbar_arrive(b_turnq + 8 * (lpar ^ 1));
           }
           LANE_ACC(5);
           mma_commit(b_kempty + 8 * kp.i);
@@ -697,18 +666,14 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
           LANE_ACC_TILE;
           TC_TRACE(23, it);
         }
-        if (!failed) mma_commit(b_qfree);  // every QK MMA of the segment has read Q (one arrival per lane)
+        if (!failed) mma_commit(b_qfree);  // every QK MMA of the segment has read Q
       }
       if (n_tiles > 0) ++sq;
       __syncwarp();
     }
     LANE_ACC_DUMP(2);
-  } else if (warp == 21 || warp == TC_WARP_PV2) {
-    // ---------------------------------------------------------------- PV issue: one lane of each of two warps
-    // The tiles of one parity each and turns at the issue, like the QK lanes. Here the order also carries the
-    // arithmetic: all PV MMAs of a segment accumulate into the same O and the softmax threads count on them running
-    // in tile order (the first overwrites O, a rescale of O sits between two of them, a tile's barrier tells that
-    // all earlier ones are done too).
+  } else if (warp == 21) {
+    // ---------------------------------------------------------------- PV issue: one lane
     // O += P V with V as an MN-major B operand covering all head dims in one instruction (N = head_dim: at 256
     // the second 128-dim slab is found through the leading-dimension stride of the descriptor).
     const uint32_t id_pv = instr_desc(TM, HD, 1);
@@ -718,7 +683,6 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
     const uint32_t b_pr = REP ? b_pready4 : b_pready;
     RingPos<C::NV> vp;  // V stage of tile `it` and (it / NV) & 1
     RingPos<NG> gp;     // softmax group of tile `it` and the parity of the group's tile count
-    const int lpar = warp == TC_WARP_PV2 ? 1 : 0;  // this lane's tiles
     LANE_ACC_DECL;
     while (read_seg(sk++, cur, true)) {
       const int n_tiles = cur.t_hi - cur.t_lo;
@@ -729,7 +693,6 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
         LANE_ACC(1);
         TC_TRACE(30, it);
         for (int t = 0; t < n_tiles; ++t, ++it, vp.advance(), gp.advance()) {
-          if (TC_PVL == 2 && (it & 1) != lpar) continue;
           TC_TRACE(37, it);
           const int g = gp.i;
           const uint64_t vb = dv + static_cast<uint64_t>(vp.i * (C::KV_BYTES >> 4));
@@ -755,11 +718,6 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
             terms = (voted || t < 2) ? 2 : 1;
           }
           TC_TRACE(35, it);
-          if (TC_PVL == 2 && it > 0) {  // my turn: the other lane has issued the tile before (its n-th tile, n = it / 2 or it / 2 - 1)
-            wait_or_flag(b_turn + 8 * lpar, static_cast<uint32_t>((it >> 1) - 1 + lpar) & 1u, failed, p.status, GA_ST_WAIT_FULL);
-            if (failed) break;
-            tc_fence_after();
-          }
 #pragma unroll 1
           for (int term = 0; term < terms; ++term) {  // hi term, then the residual term while some row needs it
             const uint64_t pa = pb + static_cast<uint64_t>(term * (PT >> 4));
@@ -767,10 +725,6 @@ attn_tc_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtens
             for (int ks = 0; ks < TNK / 32; ++ks)
               mma_f8(tmem + C::O_COL, pa + static_cast<uint64_t>(ks * 2), vb + static_cast<uint64_t>(ks * (32 * 128 >> 4)), id_pv,
                      (t > 0 || term > 0 || ks > 0) ? 1 : 0);
-          }
-          if (TC_PVL == 2) {
-            tc_fence_before();
-            mbar_arrive(b_turn + 8 * (lpar ^ 1));
           }
           TC_TRACE(36, it);
           LANE_ACC(5);
