@@ -1,5 +1,7 @@
-"""KV-range-sharded decode of one sequence on 2 GPUs (NCCL all-gather of the partials + local merge kernel)
-against the CPU oracle of the whole sequence. Skipped with fewer than two devices."""
+"""KV-range-sharded decode of one sequence on 2 GPUs against the CPU oracle of the whole sequence: the NCCL form
+(all-gather of the partials + local merge kernel) and the fused form (``kv_shard.PeerExchange``: one kernel that stores
+the partial into the peer's buffer, waits with a limit and merges), which must agree bitwise over several calls (both
+buffer parities). Skipped with fewer than two devices."""
 
 import os
 import socket
@@ -41,6 +43,13 @@ def _worker(rank, world, port, total, result_dir):
         whole, _ = attn_oracle.paged_attention(full)
         err = (out.float().cpu() - whole[0]).abs()
         ok = bool((err <= 2e-2 + 2e-2 * whole[0].abs()).all())
+        exch = kv_shard.PeerExchange(32, 128, dev)
+        for _ in range(3):  # call numbers 1, 2, 3: both halves of the double buffer
+            fused = kv_shard.decode_kv_sharded(local, exchange=exch).clone()
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(fused, out))
+        exch.check_status()
+        ok = ok and exch.epoch.tolist() == [3, 0]
         with open(os.path.join(result_dir, f"rank{rank}.txt"), "w") as f:
             f.write(f"{int(ok)} {err.max().item()}")
     finally:
