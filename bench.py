@@ -436,7 +436,7 @@ def bench_long_context(dev, rank, world, steps=20, total_tokens=1 << 20, check_t
         us = graph_us if graph_us is not None else eager_us
         res.update({"us_per_call": us, "us_per_call_eager": eager_us,
                     "issued_as": "cuda graph replay" if graph_us is not None else "eager calls",
-                    "exchange": "one kernel: peer stores of the 33 KB partial into every rank's buffer, flag, bounded wait, merge",
+                    "exchange": "one kernel: peer stores of the 33 KB partial into every rank's buffer as (value, call number) pairs, bounded poll, merge",
                     "nccl_path": {"us_per_call": nccl_us, "us_per_call_eager": nccl_eager_us,
                                   "exchange": "NCCL all-gather of 33 KB per rank + merge kernel"},
                     "same_result_as_nccl_path": agree(bool(torch.equal(out_f, out)))})

@@ -603,22 +603,20 @@ int ga_attn_merge(const GaMergeParams* m, void* stream) {
 }
 
 int ga_attn_exchange_merge(const GaExchangeParams* x, void* stream) {
-  if (!x || !x->mine || !x->peer_bufs || !x->peer_flags || !x->epoch || !x->out || !x->status) return fail("null params");
+  if (!x || !x->mine || !x->peer_bufs || !x->epoch || !x->out || !x->status) return fail("null params");
   if (x->world < 1 || x->world > ga::kvx::MAX_WORLD) return fail("world %d outside 1..%d", x->world, ga::kvx::MAX_WORLD);
   if (x->rank < 0 || x->rank >= x->world) return fail("rank %d outside the world of %d", x->rank, x->world);
   if (x->rows <= 0 || x->head_dim <= 0) return fail("bad merge shape");
   ga::kvx::ExchDev d;
   d.mine = x->mine;
-  d.bufs = static_cast<float* const*>(x->peer_bufs);
-  d.flags = static_cast<unsigned* const*>(x->peer_flags);
+  d.bufs = static_cast<uint2* const*>(x->peer_bufs);
   d.epoch = static_cast<unsigned*>(x->epoch);
   d.rank = x->rank, d.world = x->world, d.rows = x->rows, d.hd = x->head_dim;
   d.out = static_cast<__nv_bfloat16*>(x->out);
   d.lse = x->lse;
   d.status = x->status;
   d.max_polls = x->wait_polls ? x->wait_polls : (1u << 23);
-  ga::kvx::exchange_merge_kernel<<<x->rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(d);
-  GA_CUDA(cudaGetLastError());
+  GA_CUDA(launch_pdl(ga::kvx::exchange_merge_kernel, dim3(x->rows), dim3(128), 0, static_cast<cudaStream_t>(stream), d));
   g_launches = 1;
   return 0;
 }

@@ -14,8 +14,8 @@ No kernel reads another GPU's memory and nothing on this path uses multicast loa
 bound, so both tensors travel in one packed buffer (one collective per call).
 
 ``PeerExchange`` replaces steps 2 and 3 by ONE kernel (``ga_attn_exchange_merge``): every rank stores its partial
-into the peers' gather buffers with plain peer stores, publishes it with a flag, waits (bounded) for the peers'
-rows and merges, so the collective's launch and latency and the second kernel drop out of a step that is all
+into the peers' gather buffers with plain peer stores (each float with its call number in one 8-byte store, so no
+fence and no flag), polls (bounded) for the peers' rows and merges, so the collective's launch and latency and the second kernel drop out of a step that is all
 latency. The buffers are torch symmetric memory (ordinary device memory mapped into every process of the group;
 multicast is switched off). Without it (CPU ranks, a group that cannot map peer memory) the NCCL path stays.
 """
@@ -56,8 +56,8 @@ def unpack_partials(buf: torch.Tensor, world: int, rows: int, hd: int):
 
 
 class PeerExchange:
-    """Buffers and state of the fused exchange + merge for one (group, rows, head_dim): a gather buffer and a flag
-    array in symmetric memory, the device arrays of peer pointers, the call counter and a status word.
+    """Buffers and state of the fused exchange + merge for one (group, rows, head_dim): a gather buffer in symmetric
+    memory, the device array of its peer pointers, the call counter and a status word.
     Construction is collective over ``group`` (every rank, same arguments). ``merge(mine)`` is what a decode step
     calls; it allocates nothing and can be captured in a CUDA graph (every rank must replay the same calls)."""
 
@@ -74,14 +74,11 @@ class PeerExchange:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.wait_polls = int(wait_polls)
         n = self.rows * (self.head_dim + 1)
-        self.buf = symm_mem.empty(2 * self.world * n, dtype=torch.float32, device=self.device)
-        self.flags = symm_mem.empty(2 * self.world * self.rows, dtype=torch.int32, device=self.device)
+        # every float travels as an 8-byte (value, call number) pair: [2 parities][world][n][2] 32-bit words
+        self.buf = symm_mem.empty(2 * self.world * n * 2, dtype=torch.int32, device=self.device)
         self.buf.zero_()
-        self.flags.zero_()
         self._buf_hdl = symm_mem.rendezvous(self.buf, group)
-        self._flag_hdl = symm_mem.rendezvous(self.flags, group)
         self.buf_ptrs = torch.tensor(list(self._buf_hdl.buffer_ptrs), dtype=torch.int64, device=self.device)
-        self.flag_ptrs = torch.tensor(list(self._flag_hdl.buffer_ptrs), dtype=torch.int64, device=self.device)
         self.epoch = torch.zeros(2, dtype=torch.int32, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.out = torch.empty((self.rows, self.head_dim), dtype=torch.bfloat16, device=self.device)
@@ -96,7 +93,7 @@ class PeerExchange:
         if mine.dtype != torch.float32 or mine.numel() != self.rows * (self.head_dim + 1) or not mine.is_contiguous():
             raise ValueError("PeerExchange.merge: a dense fp32 partial of rows * (head_dim + 1) elements is expected")
         x = _C.GaExchangeParams()
-        x.mine, x.peer_bufs, x.peer_flags = mine.data_ptr(), self.buf_ptrs.data_ptr(), self.flag_ptrs.data_ptr()
+        x.mine, x.peer_bufs, x.peer_flags = mine.data_ptr(), self.buf_ptrs.data_ptr(), None
         x.epoch, x.rank, x.world, x.rows, x.head_dim = self.epoch.data_ptr(), self.rank, self.world, self.rows, self.head_dim
         x.out, x.lse, x.status, x.wait_polls = self.out.data_ptr(), None, self.status.data_ptr(), self.wait_polls
         with torch.cuda.device(self.device):

@@ -83,12 +83,12 @@ typedef struct GaMergeParams {
 
 /* The same merge with the exchange of the partials inside the kernel, for one process per GPU: every rank stores
  * its packed partial ([rows * head_dim] O then [rows] natural-log LSE, fp32) into a slot of every peer's gather
- * buffer with peer stores, publishes it with a flag, waits (bounded) for the peers' rows and merges. `peer_bufs` and
- * `peer_flags` are DEVICE arrays of `world` pointers: entry j is rank j's gather buffer / flag array as mapped
- * into this process (entry `rank` is the local one). A gather buffer holds 2 * world * rows * (head_dim + 1)
- * floats, a flag array 2 * world * rows 32-bit words, `epoch` two 32-bit words; all zeroed once, on every rank,
- * before the first call, and used by no one else. Every rank must make the same sequence of calls. A wait that
- * runs out (about `wait_polls` x 0.1 us; 0 = 2^23) sets *status to 6 and the call still returns.
+ * buffer with peer stores, each float as an 8-byte (value, call number) pair, polls (bounded) its own buffer for the
+ * peers' rows and merges. `peer_bufs` is a DEVICE array of `world` pointers: entry j is rank j's gather buffer as
+ * mapped into this process (entry `rank` is the local one). A gather buffer holds 2 * world * rows * (head_dim + 1)
+ * pairs (8 bytes each), `epoch` two 32-bit words; all zeroed once, on every rank, before the first call, and used by
+ * no one else. Every rank must make the same sequence of calls. A wait that runs out (about `wait_polls` x 0.05 us
+ * per value; 0 = 2^23) sets *status to 6 and the call still returns. `peer_flags` is not used (kept for layout).
  * No counterpart in the reference (single GPU only). */
 typedef struct GaExchangeParams {
   const float* mine;

@@ -1,10 +1,10 @@
 """The fused exchange + merge kernel of the KV-range-sharded decode (``ga_attn_exchange_merge``) on ONE GPU.
 
 The kernel of rank r stores into its peers' buffers and waits for their flags. On one GPU the peers are plain
-buffers of the same device that the test fills the way the peers' kernels would have (their rows and flags are in
+buffers of the same device that the test fills the way the peers' kernels would have (their rows are in
 place before the launch, so the launched kernel never waits for another kernel); what is checked is the addressing
-of the pushes, the flag protocol over two calls (both buffer parities), the call counter and the merge against
-``ga_attn_merge``. The bounded wait is checked by a flag that nothing sets: the kernel returns and leaves status 6.
+of the pushes, the (value, call number) pairs over three calls (both buffer parities), the call counter and the merge against
+``ga_attn_merge``. The bounded wait is checked by rows that nothing writes: the kernel returns and leaves status 6.
 The two-process form over real peer memory runs in ``bench.py --gpus N`` (its result is compared bitwise with the
 NCCL path and against the oracle there).
 """
@@ -44,10 +44,9 @@ class Peers:
 
     def __init__(self, world, rank, dev):
         self.world, self.rank, self.dev = world, rank, dev
-        self.bufs = [torch.zeros(2 * world * N, dtype=torch.float32, device=dev) for _ in range(world)]
-        self.flags = [torch.zeros(2 * world * ROWS, dtype=torch.int32, device=dev) for _ in range(world)]
+        # a value and the number of the call that wrote it, side by side: [parity][source rank][element][2]
+        self.bufs = [torch.zeros(2 * world * N * 2, dtype=torch.int32, device=dev) for _ in range(world)]
         self.buf_ptrs = torch.tensor([b.data_ptr() for b in self.bufs], dtype=torch.int64, device=dev)
-        self.flag_ptrs = torch.tensor([f.data_ptr() for f in self.flags], dtype=torch.int64, device=dev)
         self.epoch = torch.zeros(2, dtype=torch.int32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.out = torch.empty(ROWS, HD, dtype=torch.bfloat16, device=dev)
@@ -55,12 +54,13 @@ class Peers:
     def arrive(self, src, call, part):
         """What rank `src`'s kernel of call number `call` leaves in rank `rank`'s buffer and flags."""
         par = call & 1
-        self.bufs[self.rank].view(2, self.world, N)[par, src].copy_(part)
-        self.flags[self.rank].view(2, self.world, ROWS)[par, src].fill_(call)
+        slot = self.bufs[self.rank].view(2, self.world, N, 2)[par, src]
+        slot[:, 0].copy_(part.view(torch.int32))
+        slot[:, 1].fill_(call)
 
     def launch(self, mine, polls=0):
         x = _C.GaExchangeParams()
-        x.mine, x.peer_bufs, x.peer_flags = mine.data_ptr(), self.buf_ptrs.data_ptr(), self.flag_ptrs.data_ptr()
+        x.mine, x.peer_bufs, x.peer_flags = mine.data_ptr(), self.buf_ptrs.data_ptr(), None
         x.epoch, x.rank, x.world, x.rows, x.head_dim = self.epoch.data_ptr(), self.rank, self.world, ROWS, HD
         x.out, x.lse, x.status, x.wait_polls = self.out.data_ptr(), None, self.status.data_ptr(), polls
         _C.check(_C.lib().ga_attn_exchange_merge(ctypes.byref(x), torch.cuda.current_stream().cuda_stream), "exchange")
@@ -95,11 +95,12 @@ def test_pushes_flags_and_merge_over_two_calls(world, rank):
         for j in range(world):
             if j == rank:
                 continue
-            # my partial sits in slot [par][rank] of every peer's buffer, my flags carry the call number
-            assert torch.equal(p.bufs[j].view(2, world, N)[par, rank], parts[rank])
-            assert (p.flags[j].view(2, world, ROWS)[par, rank] == call).all()
+            # my partial sits in slot [par][rank] of every peer's buffer, every value with the call number
+            mine_there = p.bufs[j].view(2, world, N, 2)[par, rank]
+            assert torch.equal(mine_there[:, 0].contiguous().view(torch.float32), parts[rank])
+            assert (mine_there[:, 1] == call).all()
             # and nothing else of the peer's buffer was touched
-            other = p.bufs[j].view(2, world, N).clone()
+            other = p.bufs[j].view(2, world, N, 2).clone()
             other[par, rank] = 0
             if call >= 2:
                 other[1 - par, rank] = 0  # the call before
@@ -125,7 +126,7 @@ def test_rejects_bad_arguments():
     dev = torch.device("cuda")
     p = Peers(2, 0, dev)
     x = _C.GaExchangeParams()
-    x.mine, x.peer_bufs, x.peer_flags = partial(1, dev).data_ptr(), p.buf_ptrs.data_ptr(), p.flag_ptrs.data_ptr()
+    x.mine, x.peer_bufs, x.peer_flags = partial(1, dev).data_ptr(), p.buf_ptrs.data_ptr(), None
     x.epoch, x.rank, x.world, x.rows, x.head_dim = p.epoch.data_ptr(), 2, 2, ROWS, HD
     x.out, x.status = p.out.data_ptr(), p.status.data_ptr()
     assert _C.lib().ga_attn_exchange_merge(ctypes.byref(x), None) != 0
