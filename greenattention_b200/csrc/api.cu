@@ -437,7 +437,14 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
   // Speculative verify with more than 16 rows per kv head runs on the persistent tcgen05 kernel: the same
   // tile-stream split as the warp-level kernel (128-key tiles, one CTA per SM, partials merged by the combine
   // kernel), so it balances at any batch.
-  if (rows > 16 && !a->out_is_f32 && tc_aligned(a, d)) {
+  // Rows per kv head from which a call takes the tcgen05 kernel. The warp-level MMA of e4m3 runs at the f16 rate
+  // with conversions on top on this part, so wherever the tcgen05 kernel applies it wins although at most 32 of its
+  // 128 rows are query rows (measured, B=64 x 8 192 tokens: head_dim 256 one token GQA 2 585 -> 357 us and GQA 6
+  // 325 -> 200 us; head_dim 128 with 12 or 16 rows 338 -> 226 us). At head_dim 128 up to 8 rows stay on the stream-
+  // bound kernels above / below (all-heads boxes, ganged per-head gather), which are at the copy bandwidth.
+  static const int tc_min_rows_256 = [] { const char* e = std::getenv("GREEN_ATTN_TC_MIN_ROWS_256"); return e ? std::atoi(e) : 1; }();
+  static const int tc_min_rows_128 = [] { const char* e = std::getenv("GREEN_ATTN_TC_MIN_ROWS_128"); return e ? std::atoi(e) : 9; }();
+  if (rows >= (a->head_dim == 256 ? tc_min_rows_256 : tc_min_rows_128) && a->head_dim != 512 && !a->out_is_f32 && tc_aligned(a, d)) {
     const bool rep = rows <= 32;
     const AttnInstance* tk = rep ? verify_tc_instance(a->head_dim) : extend_tc_instance(a->head_dim);
     d.tc_mode = 0;

@@ -1,10 +1,12 @@
 """``ga_attn_decode_noalloc`` (the decode entry point for hosts that cannot supply a workspace) against
 ``ga_attn_decode`` on the same inputs, through the C ABI.
 
-The two entry points launch the same kernels; only the scratch differs (a fixed array inside the library
-versus the caller's workspace), so their outputs must agree to the bit. Two different calls are made in a
-row because the built-in array keeps the previous call's contents: a stale split plan or partial slot would
-show up in the second one. The file is named to be collected last.
+Where the two entry points launch the same kernels (head_dim 128 with at most 8 rows per kv head) only the
+scratch differs (a fixed array inside the library versus the caller's workspace), so their outputs must agree
+to the bit. For the other shapes the workspace entry point takes the tcgen05 kernel while this one keeps the
+warp-level kernel: two implementations of the same math, which must agree far inside the tolerance. Different
+calls are made in a row because the built-in array keeps the previous call's contents: a stale split plan or
+partial slot would show up in the next one. The file is named to be collected last.
 """
 
 import ctypes
@@ -45,8 +47,16 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row():
     for kw_cpu in (first, second, third, fourth):
         kw = W.case_to(kw_cpu, "cuda")
         (out, lse), (ref_out, ref_lse) = _both(kw)
-        assert torch.equal(out, ref_out)
-        assert torch.equal(lse, ref_lse)
+        rows = kw["max_seqlen_q"] * (kw["q"].shape[1] // kw["k_cache"].shape[2])
+        if kw["q"].shape[2] == 128 and rows <= 8:
+            assert torch.equal(out, ref_out)
+            assert torch.equal(lse, ref_lse)
+        else:
+            diff = (out.float() - ref_out.float()).abs()
+            assert (diff <= 5e-3 + 1e-2 * ref_out.float().abs()).all()  # a bf16 step of the larger outputs at most
+            fin = torch.isfinite(ref_lse)
+            assert torch.equal(torch.isfinite(lse), fin)
+            assert (lse[fin] - ref_lse[fin]).abs().max().item() <= 2e-3
         # the status word of the built-in array is readable after the call (and says the call was clean)
         assert attn_decode.workspace_status(dev, builtin=True) == 0
         ref_o, _ = attn_oracle.paged_attention(kw_cpu)
