@@ -309,6 +309,30 @@ def bench_attn_paths(dev, hbm_gbs, bf16_tflops, flush, calls=20, check=True):
                 out[name]["parity"] = attn_parity(kw, o, [3])
         del kw, o
         torch.cuda.empty_cache()
+    # The reference's other instance shapes (green_attention/attn_decode.py:58-62), decode step, B=64 x 8 192 tokens:
+    # head_dim 256 with GQA 6 and with GQA 2 under a 1 024-token window, head_dim 512 with GQA 8. HBM-bound.
+    shapes = {}
+    for name, H, win in (("hd256_gqa6", dict(q_heads=24, kv_heads=4, head_dim=256), None),
+                         ("hd256_gqa2_window1024", dict(q_heads=16, kv_heads=8, head_dim=256), (1023, 0)),
+                         ("hd512_gqa8", dict(q_heads=32, kv_heads=4, head_dim=512), None)):
+        extra = {"window": win} if win else {}
+        kw = W.make_paged_case([8192] * 64, [1] * 64, 64, seed=13, device=dev, kv_std=0.5, descale="rand",
+                               return_lse=False, **H, **extra)
+        st, o = timed(kw, attn_decode.select)
+        if o is None:
+            shapes[name] = st
+        else:
+            nb, med = W.attn_kv_bytes(kw), st["median_us"] * 1e-6
+            shapes[name] = {"workload": f"decode B=64 x 8192 tokens, QH{H['q_heads']}/KVH{H['kv_heads']}, hd{H['head_dim']}, page 64"
+                                        + (f", window {win[0] + 1}" if win else ""),
+                            "us_per_call": st["median_us"], "stats": st,
+                            "roofline": {"bound": "hbm", "achieved": nb / med / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                                         "frac": nb / med / 1e9 / hbm_gbs, "algorithmic_bytes": nb}}
+            if check:
+                shapes[name]["parity"] = attn_parity(kw, o, [0, 63])
+        del kw, o
+        torch.cuda.empty_cache()
+    out["instance_shapes"] = shapes
     out["status_word"] = attn_decode.workspace_status(dev)
     return out
 
