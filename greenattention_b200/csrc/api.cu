@@ -434,9 +434,8 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
   d.max_q = a->max_seqlen_q;
   d.bq = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // Speculative verify with more than 16 rows per kv head runs on the persistent tcgen05 kernel: the same
-  // tile-stream split as the warp-level kernel (128-key tiles, one CTA per SM, partials merged by the combine
-  // kernel), so it balances at any batch.
+  // The persistent tcgen05 kernel in split mode: the same tile-stream split as the warp-level kernel (128-key tiles,
+  // one CTA per SM, partials merged by the combine kernel), so it balances at any batch.
   // Rows per kv head from which a call takes the tcgen05 kernel. The warp-level MMA of e4m3 runs at the f16 rate
   // with conversions on top on this part, so wherever the tcgen05 kernel applies it wins although at most 32 of its
   // 128 rows are query rows (measured, B=64 x 8 192 tokens: head_dim 256 one token GQA 2 585 -> 357 us and GQA 6
