@@ -434,3 +434,31 @@ def test_ganged_verify_route_in_a_fresh_process():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "ganged ok" in res.stdout, res.stderr[-2000:]
+
+
+def test_warp_level_route_of_the_shapes_the_tcgen05_kernel_takes_by_default():
+    """``GREEN_ATTN_TC_MIN_ROWS_128 / _256 = 17`` (read once per process) keep head_dim 256 decode and 9 - 16 rows at
+    head_dim 128 on the warp-level instances: still product code (it is what pools with tiny pages, unaligned rows and
+    the no-workspace entry point run for these shapes). Same bar."""
+    import subprocess
+    import sys
+
+    code = (
+        "import torch, sys; sys.path.insert(0, '.');"
+        "from greenattention_b200 import attn_decode, workloads as W;"
+        "from oracle import attn_oracle;"
+        "attn_decode.ensure_ready();"
+        "cases=[W.make_paged_case([9000, 300, 5, 40000, 0, 777], [1]*6, 64, q_heads=12, kv_heads=2, head_dim=256, seed=7, descale='rand', kv_std=0.5),"
+        " W.make_paged_case([3000, 64, 12000], [2]*3, 64, q_heads=16, kv_heads=2, head_dim=128, seed=8, window=(511, 0)),"
+        " W.make_paged_case([700, 129, 5000], [3]*3, 16, q_heads=8, kv_heads=2, head_dim=256, seed=9)];\n"
+        "for c in cases:\n"
+        "    kw = W.case_to(c, 'cuda'); out, lse = attn_decode.select(kw)(**kw); torch.cuda.synchronize()\n"
+        "    ref, ref_lse = attn_oracle.paged_attention(c)\n"
+        "    assert ((out.float().cpu() - ref).abs() <= 2e-2 + 2e-2 * ref.abs()).all()\n"
+        "    fin = torch.isfinite(ref_lse); assert (lse.cpu()[fin] - ref_lse[fin]).abs().max() <= 5e-3\n"
+        "assert attn_decode.workspace_status(torch.device('cuda', 0)) == 0; print('warp-level ok')"
+    )
+    env = dict(os.environ, GREEN_ATTN_TC_MIN_ROWS_128="17", GREEN_ATTN_TC_MIN_ROWS_256="17")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "warp-level ok" in res.stdout, res.stderr[-2000:]
