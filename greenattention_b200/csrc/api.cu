@@ -213,7 +213,9 @@ int set_smem(const AttnInstance& k) {
 
 // Raises the dynamic shared memory limit of every kernel instance on the current device.
 int set_all_smem_limits() {
-  GA_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(ga::attn::attn_wide_kernel),
+  GA_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(ga::attn::attn_wide_kernel<ga::attn::WIDE_T>),
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, ga::attn::SMEM_OPTIN));
+  GA_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(ga::attn::attn_wide_kernel<ga::attn::WIDE_T / 2>),
                                cudaFuncAttributeMaxDynamicSharedMemorySize, ga::attn::SMEM_OPTIN));
   if (set_smem(*decode_instance(512, 8))) return 1;
   for (int hd : {128, 256}) {
@@ -464,19 +466,24 @@ int ga_attn_decode(const GaAttnParams* a, void* stream) {
     return 0;
   }
   dim3 cgrid(a->batch, a->kv_heads, combine_z(a->batch * a->kv_heads, rows, sm));
-  // The production decode shape (at most 8 rows per kv head, head_dim 128, 4..8 kv heads, pages of at least 32
+  // The production decode shape (at most 8 rows per kv head, head_dim 128, 4..8 kv heads, pages of at least 16
   // tokens) gathers all kv heads of a token run per TMA box: contiguous 16 - 32 KB runs of a page stream about a
   // fifth faster than one head's 128-byte pieces. GREEN_ATTN_NO_WIDE=1 keeps such calls on the per-head kernel.
   static const bool no_wide = [] { const char* e = std::getenv("GREEN_ATTN_NO_WIDE"); return e && e[0] == '1'; }();
-  if (!no_wide && rows <= 8 && a->head_dim == 128 && d.use_tma && a->page_size >= ga::attn::WIDE_T && a->kv_heads >= 4 &&
+  if (!no_wide && rows <= 8 && a->head_dim == 128 && d.use_tma && a->page_size >= ga::attn::WIDE_T / 2 && a->kv_heads >= 4 &&
       a->kv_heads <= ga::attn::WIDE_HEADS) {
+    const int wide_box = a->page_size >= ga::attn::WIDE_T ? ga::attn::WIDE_T : ga::attn::WIDE_T / 2;
     MapKey kk = {a->k_cache, a->k_stride_page, a->k_stride_tok, a->k_stride_head, a->num_pages, a->page_size,
-                 a->kv_heads, a->head_dim, ga::attn::WIDE_T, 1};
+                 a->kv_heads, a->head_dim, wide_box, 1};
     MapKey vk = {a->v_cache, a->v_stride_page, a->v_stride_tok, a->v_stride_head, a->num_pages, a->page_size,
-                 a->kv_heads, a->head_dim, ga::attn::WIDE_T, 1};
+                 a->kv_heads, a->head_dim, wide_box, 1};
     if (get_map(kk, &kmap) || get_map(vk, &vmap)) return 1;
-    GA_CUDA(launch_pdl(ga::attn::attn_wide_kernel, dim3(sm), dim3(ga::attn::WIDE_THREADS),
-                       static_cast<size_t>(ga::attn::wide_smem_bytes(a->kv_heads)), st, d, kmap, vmap));
+    if (wide_box == ga::attn::WIDE_T)
+      GA_CUDA(launch_pdl(ga::attn::attn_wide_kernel<ga::attn::WIDE_T>, dim3(sm), dim3(ga::attn::WIDE_THREADS),
+                         static_cast<size_t>(ga::attn::wide_smem_bytes(a->kv_heads)), st, d, kmap, vmap));
+    else
+      GA_CUDA(launch_pdl(ga::attn::attn_wide_kernel<ga::attn::WIDE_T / 2>, dim3(sm), dim3(ga::attn::WIDE_THREADS),
+                         static_cast<size_t>(ga::attn::wide_smem_bytes(a->kv_heads)), st, d, kmap, vmap));
     GA_CUDA(launch_pdl(ga::attn::attn_combine_kernel<128>, cgrid, dim3(128), 0, st, d, sm, ga::attn::WIDE_ROWS, ga::attn::WIDE_T, 1));
     g_launches = 2;
     return 0;

@@ -716,11 +716,12 @@ __device__ __forceinline__ void load_q_frags8(const AttnDev& p, const Seg& s, in
 }
 
 // NT: tokens of the tile (a multiple of 32); K rows at `k_addr`, V rows at `v_addr`, each NT x 128 bytes per
-// 128-dim slab, swizzled by token.
+// 128-dim slab, swizzled by token. `hop`: extra bytes between token 15 and token 16 (a tile that arrived as two
+// 16-token boxes whose halves of one head do not follow each other); 0 for every other caller.
 template <class C, int NT = TN>
 __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, int n0, uint32_t k_addr, uint32_t v_addr,
                                               const uint32_t (&qf)[C::ATOMS * 4][2], int pos, float sl2,
-                                              RowAcc8<C>& acc, int lane, int dsel = 0) {
+                                              RowAcc8<C>& acc, int lane, int dsel = 0, uint32_t hop = 0) {
   static_assert(NT % 32 == 0, "tile length");
   constexpr int SLABB = NT * 128;  // bytes between the 128-dim slabs of a wider head
   constexpr int NG = NT / 8;       // 8-token groups
@@ -741,7 +742,7 @@ __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, in
       uint32_t kb[4][2][4];
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
-        const uint32_t rowaddr = k_addr + slab * SLABB + ((half * 4 + jj) * 8 + lrow) * 128;
+        const uint32_t rowaddr = k_addr + slab * SLABB + ((half * 4 + jj) * 8 + lrow) * 128 + ((half * 4 + jj) >= 2 ? hop : 0u);
 #pragma unroll
         for (int q2 = 0; q2 < 2; ++q2) {
           const int c = q2 * 4 + lmat;  // 16-byte chunk of the slab
@@ -782,7 +783,7 @@ __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, in
       if (first < 0) first = 0;
       for (int idx = first * (C::ATOMS * 8) + lane; idx < NT * C::ATOMS * 8; idx += 32) {
         int row = idx / (C::ATOMS * 8), c = idx - row * (C::ATOMS * 8);
-        uint32_t a = v_addr + (c >> 3) * SLABB + row * 128 + ((c & 7) << 4);
+        uint32_t a = v_addr + (c >> 3) * SLABB + row * 128 + ((c & 7) << 4) + (row >= 16 ? hop : 0u);
         asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0) : "memory");
       }
       __syncwarp();
@@ -829,7 +830,7 @@ __device__ __forceinline__ void consume_tile8(const AttnDev& p, const Seg& s, in
   for (int c2 = 0; c2 < NT / 32; ++c2) {
     const uint32_t bh0 = ph[c2 * 4] | (ph[c2 * 4 + 1] << 16), bh1 = ph[c2 * 4 + 2] | (ph[c2 * 4 + 3] << 16);
     const uint32_t bl0 = pl[c2 * 4] | (pl[c2 * 4 + 1] << 16), bl1 = pl[c2 * 4 + 2] | (pl[c2 * 4 + 3] << 16);
-    const uint32_t rowaddr = vbase + ((c2 * 4 + lmat) * 8 + lrow) * 128;
+    const uint32_t rowaddr = vbase + ((c2 * 4 + lmat) * 8 + lrow) * 128 + ((c2 * 4 + lmat) >= 2 ? hop : 0u);
 #pragma unroll
     for (int grp = 0; grp < C::ATOMS / C::DS; ++grp) {  // eight 16-dim blocks at a time; slabs of this warp's share
       uint32_t va[8][4];

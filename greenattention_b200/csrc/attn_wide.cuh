@@ -38,9 +38,13 @@ __host__ __device__ constexpr int wide_stages(int kvh) {
 }
 __host__ __device__ constexpr int wide_smem_bytes(int kvh) { return 1024 + wide_stages(kvh) * wide_stage_bytes(kvh) + 1024; }
 
+// BOX: tokens per TMA box, 32 (one box per tile) or 16 (pools with 16-token pages: two boxes per tile). A template
+// parameter so that the 32-token form carries none of the second box's arithmetic.
+template <int BOX>
 __global__ void __launch_bounds__(WIDE_THREADS, 1)
 attn_wide_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap) {
+  static_assert(BOX == WIDE_T || BOX * 2 == WIDE_T, "box size");
   using C = Cfg<128, 1, 1, 1, 2, 1>;  // head_dim 128: fragment shapes of the 8-row path
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -84,18 +88,25 @@ attn_wide_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
           if (lane == 0) atomicExch(p.status, GA_ST_WAIT_EMPTY);
           return;
         }
-        // a tile never straddles a page (pages hold a multiple of WIDE_T tokens) and the whole box is in the page,
-        // so a stage always receives its full byte count; tokens past the end of the sequence are masked later
+        // A box never straddles a page (pages hold a multiple of its tokens) and lies in the page as a whole. A
+        // tile is one box of 32 tokens or, on 16-token pages, two boxes of 16 from two pages; a second box that
+        // starts past the end of the sequence is not asked for (its page-table entry may be padding). Tokens past
+        // the end of the sequence inside a box are masked later.
         const int n0 = tt * WIDE_T;
-        int page = pt_lookup(p, win, s.b, n0 >> p.page_shift, lane);
-        if (page < 0 || page >= p.num_pages) {
-          if (lane == 0) atomicExch(p.status, GA_ST_BAD_PAGE);  // recorded; an out-of-range box reads as zeros
-        }
-        if (lane == 0) mbar_expect_tx(bars + stage * 8, static_cast<uint32_t>(stage_bytes));
+        const int nbx = (BOX < WIDE_T && n0 + BOX < s.L) ? 2 : 1;
+        const int box_bytes = kvh * BOX * 128;
+        if (lane == 0) mbar_expect_tx(bars + stage * 8, static_cast<uint32_t>(2 * nbx * box_bytes));
         __syncwarp();
-        if (lane < 2) {
-          const uint32_t dst = ring + stage * stage_bytes + lane * (stage_bytes / 2);
-          tma_load_4d(dst, lane ? &vmap : &kmap, bars + stage * 8, 0, n0 & p.page_mask, 0, page);
+        for (int i = 0; i < nbx; ++i) {
+          const int n = n0 + i * BOX;
+          int page = pt_lookup(p, win, s.b, n >> p.page_shift, lane);
+          if (page < 0 || page >= p.num_pages) {
+            if (lane == 0) atomicExch(p.status, GA_ST_BAD_PAGE);  // recorded; an out-of-range box reads as zeros
+          }
+          if (lane < 2) {
+            const uint32_t dst = ring + stage * stage_bytes + lane * (stage_bytes / 2) + i * box_bytes;
+            tma_load_4d(dst, lane ? &vmap : &kmap, bars + stage * 8, 0, n & p.page_mask, 0, page);
+          }
         }
       }
     }
@@ -105,6 +116,7 @@ attn_wide_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
 
   // -------------------------------------------------------------------- consumer warp = kv head
   const int g = lane >> 2, t = lane & 3;
+  const uint32_t hop = BOX == WIDE_T ? 0u : static_cast<uint32_t>((kvh - 1) * BOX * 128);
   RowAcc8<C> acc;
   uint32_t qf[4][2];
   int pos;
@@ -124,8 +136,9 @@ attn_wide_kernel(const __grid_constant__ AttnDev p, const __grid_constant__ CUte
         failed = true;
       }
       if (failed) continue;
-      const uint32_t k_addr = ring + stage * stage_bytes + warp * (WIDE_T * 128);
-      consume_tile8<C, WIDE_T>(p, sw, tt * WIDE_T, k_addr, k_addr + stage_bytes / 2, qf, pos, sl2, acc, lane);
+      // head `warp` of a box is BOX tokens x 128 bytes; with two boxes its second 16 tokens sit a box further
+      const uint32_t k_addr = ring + stage * stage_bytes + warp * (BOX * 128);
+      consume_tile8<C, WIDE_T>(p, sw, tt * WIDE_T, k_addr, k_addr + stage_bytes / 2, qf, pos, sl2, acc, lane, 0, hop);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + (nst + stage) * 8);

@@ -1,5 +1,5 @@
 """The all-heads decode kernel (``attn_wide_kernel``: one query token, head_dim 128, 4..8 kv heads, pages of at
-least 32 tokens, every TMA box holding all kv heads of a token run) on the GPU against the CPU oracle, through the
+least 16 tokens, every TMA box holding all kv heads of a token run; two boxes per tile on 16-token pages) on the GPU against the CPU oracle, through the
 plugin front-end and the C ABI. The matrix is the decode part of the reference's op tests
 (``op_test/sm90/test_attn_decode_fp8.py:219-365``) on the shapes this kernel takes; everything else stays on the
 per-head kernel, which ``tests/test_attn_gpu.py`` covers.
@@ -34,10 +34,23 @@ def _ready():
 
 
 @pytest.mark.parametrize("inst", [KVH8_G8, KVH8_G4, KVH4_G8, KVH6_G2, KVH5_G1], ids=["kvh8g8", "kvh8g4", "kvh4g8", "kvh6g2", "kvh5g1"])
-@pytest.mark.parametrize("page", [32, 64, 128])
+@pytest.mark.parametrize("page", [16, 32, 64, 128])
 @pytest.mark.parametrize("q_dtype", [FP8, torch.bfloat16])
 def test_ragged_lengths(inst, page, q_dtype):
     check(W.make_paged_case(LENS, [1] * len(LENS), page, q_dtype=q_dtype, seed=page + inst["kv_heads"], descale="rand", **inst))
+
+
+@pytest.mark.parametrize("L", [1, 15, 16, 17, 31, 32, 33, 47, 48, 49, 4736, 65536])
+def test_sixteen_token_pages_around_box_and_tile_ends(L):
+    """Two 16-token boxes per 32-token tile; a sequence that ends inside the first box leaves the second one out, and
+    the page-table row is padded with an id outside the pool right behind the last page in use."""
+    kw = W.make_paged_case([L, 40, 3], [1, 1, 1], 16, seed=L % 97, extra_pages=8, descale="rand", **KVH8_G8)
+    pt = kw["page_table"]
+    used = -(-L // 16)
+    if used < pt.shape[1]:
+        pt[0, used:] = -1  # padding must never be looked at
+    check(kw)
+    check(W.make_paged_case([L, 5000], [1, 1], 16, seed=L % 89, window=(1023, 0), **KVH4_G8))
 
 
 def test_empty_sequences_and_whole_batch_empty():
