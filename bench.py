@@ -585,11 +585,15 @@ def main():
     barrier()
     e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
+    step_ms = []  # host clock per step, beside the device-timed total: shows when one slow step carries the mean
     for _ in range(args.steps):
+        t0 = time.perf_counter()
         e2e_step()
+        step_ms.append((time.perf_counter() - t0) * 1e3)
     e_stop.record()
     barrier()
     e2e_ms_total = e_start.elapsed_time(e_stop)
+    step_ms.sort()
 
     stats = torch.tensor([ms_total, e2e_ms_total, float(nbytes)], dtype=torch.float64, device=dev)
     if world > 1:
@@ -617,7 +621,8 @@ def main():
                        "partitioning": f"requests x{world}, same context-length draw on every rank", "l2": "inputs (4.4 GB/GPU) larger than the 126 MB L2"},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms_total / args.steps},
+                    "ms_per_step": e2e_ms_total / args.steps,
+                    "step_ms_host_clock_rank0": {"min": step_ms[0], "median": step_ms[len(step_ms) // 2], "max": step_ms[-1]}},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": hbm_gbs, "unit": "GB/s",
                          "frac": per_gpu_gbs / hbm_gbs, "peak_kind": f"{peak_kind} copy bandwidth",
